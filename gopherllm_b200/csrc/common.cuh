@@ -1,0 +1,72 @@
+// Shared declarations of the sm_100a kernels.
+//
+// Every launcher is an extern "C" function that takes raw device pointers, sizes
+// and the CUDA stream, launches on that stream, allocates nothing and returns 0
+// or a negative error code (see gl_error_string in the Python wrapper).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define GL_API extern "C" __attribute__((visibility("default")))
+
+// element types of buffers passed by void*
+enum GlDtype { GL_F32 = 0, GL_BF16 = 1 };
+
+// activation applied in an epilogue
+enum GlAct { GL_ACT_NONE = 0, GL_ACT_GELU_TANH = 1, GL_ACT_GELU_ERF = 2, GL_ACT_RELU = 3 };
+
+// error codes
+enum GlError {
+    GL_OK = 0,
+    GL_ERR_DTYPE = -1,      // combination of element types not built
+    GL_ERR_SHAPE = -2,      // a size the kernel does not take
+    GL_ERR_ALIGN = -3,      // a pointer or stride not aligned as required
+    GL_ERR_LAUNCH = -4,     // cudaGetLastError() after the launch was not success
+    GL_ERR_SMEM = -5,       // shared memory need exceeds the device limit
+    GL_ERR_DRIVER = -6,     // a driver entry point could not be obtained or failed
+};
+
+// tokens of the cache that share one page
+#define GL_PAGE 64
+
+static inline int gl_check_launch() {
+    return cudaGetLastError() == cudaSuccess ? GL_OK : GL_ERR_LAUNCH;
+}
+
+__device__ __forceinline__ float gl_load(const float* p) { return *p; }
+__device__ __forceinline__ float gl_load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void gl_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void gl_store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float gl_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float gl_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Activations in 32-bit.  gelu "tanh form" is x*sigmoid(2*sqrt(2/pi)*(x+0.044715x^3)),
+// the form the reference evaluates (fastmath.go:138-141); the erf form is
+// 0.5*x*(1+erf(x/sqrt(2))) (bert.go:742-744).
+template <bool EXACT>
+__device__ __forceinline__ float gl_activate(float x, int act) {
+    switch (act) {
+        case GL_ACT_GELU_TANH: {
+            const float z = 1.5957691216057308f * (x + 0.044715f * x * x * x);
+            const float e = EXACT ? expf(-z) : __expf(-z);
+            return x / (1.0f + e);
+        }
+        case GL_ACT_GELU_ERF:
+            return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+        case GL_ACT_RELU:
+            return fmaxf(x, 0.0f);
+        default:
+            return x;
+    }
+}

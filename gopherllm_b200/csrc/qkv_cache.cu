@@ -1,0 +1,132 @@
+// What happens between the QKV product and attention, in one pass over the
+// projected rows: optional per-head norm of q and k, rotary position encoding,
+// the query scale, and the write of k and v into the paged cache.
+//
+// Order as in the reference: bias (already in the product's epilogue), head
+// norm, rotation, then the query scale (model.go:2677-2706, forward_batch.go:446-469);
+// keys are cached rotated and unscaled (model.go:1466-1487).
+#include "common.cuh"
+
+// cos/sin of angle float(pos) * inv_freq[i]; the product is taken in 32-bit and
+// the functions in 64-bit, as the reference does (model.go:3041-3046).
+__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * half) return;
+    const int t = i / half, p = i % half;
+    const float a = (float)pos[t] * inv_freq[p];
+    double s, c;
+    sincos((double)a, &s, &c);
+    cosv[i] = (float)c;
+    sinv[i] = (float)s;
+}
+
+GL_API int gl_rope_table(const int* pos, const float* inv_freq, float* cosv, float* sinv,
+                         int T, int half, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return GL_OK;
+    const int n = T * half;
+    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(pos, inv_freq, cosv, sinv, T, half);
+    return gl_check_launch();
+}
+
+struct QkvCacheArgs {
+    const void* qkv;          // [T, (nH + 2 nKV) * hd], activation type
+    void* q_out;              // [T, nH * hd], activation type
+    void* k_cache;            // this cache entry's keys   [pages, nKV, GL_PAGE, hd], cache type
+    void* v_cache;            // this cache entry's values
+    const float* cosv;        // [T, half] or null
+    const float* sinv;
+    const float* q_gamma;     // [hd] or null: per-head norm of q
+    const float* q_beta;      // [hd] or null
+    const float* k_gamma;
+    const float* k_beta;
+    const int* tok_seq;       // [T] sequence of each token
+    const int* tok_pos;       // [T] absolute position of each token
+    const int* pages;         // [B, max_pages] page ids of each sequence
+    int T, nH, nKV, hd, half, max_pages;
+    int interleaved, norm_rms, write_kv;
+    float eps, q_scale;
+};
+
+template <typename TA, typename TC>
+__global__ void qkv_cache_kernel(QkvCacheArgs a) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = a.nH + 2 * a.nKV;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)a.T * heads) return;
+    const int t = (int)(item / heads), j = (int)(item % heads);
+    const int kind = j < a.nH ? 0 : (j < a.nH + a.nKV ? 1 : 2);   // q, k, v
+    if (kind != 0 && !a.write_kv) return;
+    const int hd = a.hd;
+    float* v = smem + warp * hd;
+    const TA* src = (const TA*)a.qkv + (size_t)t * heads * hd + (size_t)j * hd;
+    for (int d = lane; d < hd; d += 32) v[d] = gl_load(src + d);
+    __syncwarp();
+
+    const float* gamma = kind == 0 ? a.q_gamma : a.k_gamma;
+    const float* beta = kind == 0 ? a.q_beta : a.k_beta;
+    if (kind != 2 && gamma) {
+        float mean = 0.f;
+        if (!a.norm_rms) {
+            float s = 0.f;
+            for (int d = lane; d < hd; d += 32) s += v[d];
+            mean = gl_warp_sum(s) / (float)hd;
+        }
+        float q = 0.f;
+        for (int d = lane; d < hd; d += 32) { const float c = v[d] - mean; q += c * c; }
+        const float var = gl_warp_sum(q) / (float)hd;
+        const float inv = (float)(1.0 / sqrt((double)(var + a.eps)));
+        for (int d = lane; d < hd; d += 32) {
+            float y = (v[d] - mean) * inv * gamma[d];
+            if (beta) y += beta[d];
+            v[d] = y;
+        }
+        __syncwarp();
+    }
+    if (kind != 2 && a.half > 0 && a.cosv) {
+        const float* cs = a.cosv + (size_t)t * a.half;
+        const float* sn = a.sinv + (size_t)t * a.half;
+        for (int i = lane; i < a.half; i += 32) {
+            const int i0 = a.interleaved ? 2 * i : i;
+            const int i1 = a.interleaved ? 2 * i + 1 : i + a.half;
+            const float c = cs[i], s = sn[i];
+            const float u = v[i0], w = v[i1];
+            v[i0] = u * c - w * s;
+            v[i1] = u * s + w * c;
+        }
+        __syncwarp();
+    }
+    if (kind == 0) {
+        TA* dst = (TA*)a.q_out + (size_t)t * a.nH * hd + (size_t)j * hd;
+        for (int d = lane; d < hd; d += 32) gl_store(dst + d, v[d] * a.q_scale);
+    } else {
+        const int head = kind == 1 ? j - a.nH : j - a.nH - a.nKV;
+        const int pos = a.tok_pos[t];
+        const int page = a.pages[(size_t)a.tok_seq[t] * a.max_pages + pos / GL_PAGE];
+        TC* base = (TC*)(kind == 1 ? a.k_cache : a.v_cache);
+        TC* dst = base + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * hd;
+        for (int d = lane; d < hd; d += 32) gl_store(dst + d, v[d]);
+    }
+}
+
+GL_API int gl_qkv_cache(const QkvCacheArgs* args, int act_dtype, int cache_dtype, cudaStream_t stream) {
+    const QkvCacheArgs& a = *args;
+    if (a.T <= 0) return GL_OK;
+    if (a.hd <= 0 || a.nH <= 0 || a.nKV <= 0 || 2 * a.half > a.hd) return GL_ERR_SHAPE;
+    const int warps = 4;
+    const long long items = (long long)a.T * (a.nH + 2 * a.nKV);
+    const unsigned blocks = (unsigned)((items + warps - 1) / warps);
+    const size_t smem = (size_t)warps * a.hd * sizeof(float);
+    if (act_dtype == GL_F32 && cache_dtype == GL_F32)
+        qkv_cache_kernel<float, float><<<blocks, warps * 32, smem, stream>>>(a);
+    else if (act_dtype == GL_BF16 && cache_dtype == GL_BF16)
+        qkv_cache_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(a);
+    else if (act_dtype == GL_BF16 && cache_dtype == GL_F32)
+        qkv_cache_kernel<__nv_bfloat16, float><<<blocks, warps * 32, smem, stream>>>(a);
+    else if (act_dtype == GL_F32 && cache_dtype == GL_BF16)
+        qkv_cache_kernel<float, __nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(a);
+    else
+        return GL_ERR_DTYPE;
+    return gl_check_launch();
+}

@@ -1,0 +1,187 @@
+"""The step function: one batch of token runs through the model, from the cache.
+
+A step takes, for each sequence of the batch, its next tokens (a whole prompt, a
+piece of one, or a single token) and the places among them whose logits are
+wanted.  It runs exactly those tokens as one ragged batch (no padding exists,
+so padding cannot change a result), writes their keys and values behind what
+the cache already holds for the sequence, and returns float32 logits at the
+wanted places.  The reference has the two ends of this: a chunk of one sequence
+(ForwardBatchInto, forward_batch.go:311-318, logits for the last position only,
+:601-612) and a single token (ForwardInto, model.go:2550-2553).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.sequence_cache import SequenceCache
+from .model import DecoderModel
+
+
+class StepContext:
+    """What the parts see of a step.  Tensors are int32 on the device.
+
+    tokens[T], tok_seq[T] (index of the token's sequence in this batch),
+    tok_pos[T] (absolute position); seq_slot[B], seq_qstart[B] (row of the
+    sequence's first token), seq_qlen[B], seq_ctx[B] (positions cached before
+    the step); want_rows[M]; pages[g] = [B, max_pages] page ids in cache group g.
+    Host-side: n_tokens, n_seqs, n_want, max_qlen, max_len (longest sequence
+    after the step), is_decode (every run is one token), act_dtype, device,
+    scratch (per-step memo shared by the parts, e.g. position tables).
+    """
+
+    def __init__(self, device, act_dtype):
+        self.device, self.act_dtype = device, act_dtype
+        self.scratch: Dict = {}
+        self.pages: List[torch.Tensor] = []
+        self.tokens = self.tok_seq = self.tok_pos = None
+        self.seq_slot = self.seq_qstart = self.seq_qlen = self.seq_ctx = None
+        self.want_rows = None
+        self.n_tokens = self.n_seqs = self.n_want = 0
+        self.max_qlen = self.max_len = 0
+        self.is_decode = False
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class _Layout:
+    """Offsets of the step's arrays inside one int32 buffer (each 16-byte aligned)."""
+
+    def __init__(self, T: int, B: int, M: int, groups: int, max_pages: int):
+        self.T, self.B, self.M, self.groups, self.max_pages = T, B, M, groups, max_pages
+        o = 0
+        self.off: Dict[str, Tuple[int, int]] = {}
+        for name, n in (("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B),
+                        ("seq_qstart", B), ("seq_qlen", B), ("seq_ctx", B), ("want_rows", M)):
+            self.off[name] = (o, n)
+            o += _pad4(n)
+        for g in range(groups):
+            self.off[f"pages{g}"] = (o, B * max_pages)
+            o += _pad4(B * max_pages)
+        self.size = max(o, 4)
+
+    def key(self):
+        return (self.T, self.B, self.M, self.groups, self.max_pages)
+
+
+class Engine:
+    """Owns a model, its cache and the step function."""
+
+    def __init__(self, model: DecoderModel, cache: SequenceCache, act_dtype: torch.dtype, device):
+        self.model, self.cache = model, cache
+        self.act_dtype, self.device = act_dtype, torch.device(device)
+        self.vocab = model.spec.vocab
+        self._pinned: List[Optional[torch.Tensor]] = [None, None]
+        self._events: List[Optional[torch.cuda.Event]] = [None, None]
+        self._flip = 0
+        self.h2d_bytes_last = 0
+
+    # -- sequences ----------------------------------------------------------
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    # -- the step -------------------------------------------------------------
+    def plan(self, runs: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]]):
+        """Host-side part of a step: checks, page reservation, the packed descriptor.
+        Returns (layout, numpy int32 buffer, new lengths)."""
+        if not runs:
+            raise ValueError("a step needs at least one sequence")
+        cache = self.cache
+        slots = [int(s) for s, _ in runs]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a sequence appears twice in one step")
+        qlens = [len(t) for _, t in runs]
+        if min(qlens) < 1:
+            raise ValueError("every sequence of a step brings at least one token")
+        ctxs = [cache.length(s) for s in slots]
+        T, B = sum(qlens), len(runs)
+        if want is None:
+            want = [[q - 1] for q in qlens]
+        if len(want) != B:
+            raise ValueError("want must have one list per sequence")
+        rows: List[int] = []
+        start = 0
+        for q, w in zip(qlens, want):
+            for i in w:
+                if not 0 <= int(i) < q:
+                    raise ValueError(f"wanted place {i} is outside a run of {q} tokens")
+                rows.append(start + int(i))
+            start += q
+        cache.reserve([(s, c + q) for s, c, q in zip(slots, ctxs, qlens)])
+        lay = _Layout(T, B, len(rows), len(cache.groups), cache.max_pages_per_seq)
+        buf = np.zeros(lay.size, dtype=np.int32)
+
+        def put(name, values):
+            o, n = lay.off[name]
+            buf[o:o + n] = values
+
+        toks = np.concatenate([np.asarray(t, dtype=np.int64) for _, t in runs])
+        if toks.min() < 0 or toks.max() >= self.vocab:
+            raise ValueError(f"token id outside [0, {self.vocab})")
+        put("tokens", toks)
+        put("tok_seq", np.repeat(np.arange(B), qlens))
+        put("tok_pos", np.concatenate([np.arange(c, c + q) for c, q in zip(ctxs, qlens)]))
+        put("seq_slot", slots)
+        put("seq_qstart", np.concatenate([[0], np.cumsum(qlens)[:-1]]))
+        put("seq_qlen", qlens)
+        put("seq_ctx", ctxs)
+        put("want_rows", rows)
+        for g in range(lay.groups):
+            o, n = lay.off[f"pages{g}"]
+            cache.page_rows(g, slots, out=buf[o:o + n].reshape(B, lay.max_pages))
+        meta = dict(slots=slots, new_lens=[c + q for c, q in zip(ctxs, qlens)],
+                    max_qlen=max(qlens), is_decode=max(qlens) == 1)
+        return lay, buf, meta
+
+    def _upload(self, buf: np.ndarray) -> torch.Tensor:
+        i = self._flip
+        self._flip ^= 1
+        if self._events[i] is not None:
+            self._events[i].synchronize()          # the copy that last used this staging buffer is done
+        pin = self._pinned[i]
+        if pin is None or pin.numel() < buf.size:
+            pin = torch.empty(max(buf.size, 4096), dtype=torch.int32, pin_memory=True)
+            self._pinned[i] = pin
+        pin[:buf.size].numpy()[...] = buf
+        dev = torch.empty(buf.size, dtype=torch.int32, device=self.device)
+        dev.copy_(pin[:buf.size], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
+        self.h2d_bytes_last = buf.size * 4
+        return dev
+
+    def context(self, lay: _Layout, dev: torch.Tensor, meta: dict) -> StepContext:
+        ctx = StepContext(self.device, self.act_dtype)
+        for name in ("tokens", "tok_seq", "tok_pos", "seq_slot", "seq_qstart", "seq_qlen",
+                     "seq_ctx", "want_rows"):
+            o, n = lay.off[name]
+            setattr(ctx, name, dev[o:o + n])
+        for g in range(lay.groups):
+            o, n = lay.off[f"pages{g}"]
+            ctx.pages.append(dev[o:o + n].view(lay.B, lay.max_pages))
+        ctx.n_tokens, ctx.n_seqs, ctx.n_want = lay.T, lay.B, lay.M
+        ctx.max_qlen, ctx.is_decode = meta["max_qlen"], meta["is_decode"]
+        ctx.max_len = max(meta["new_lens"])
+        return ctx
+
+    @torch.no_grad()
+    def step(self, runs: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """runs: [(slot, tokens)]; want[b]: places in run b whose logits are wanted
+        (default: the last token of every run).  Returns float32 [wanted, vocab] on
+        the device, in the order of runs and of want."""
+        lay, buf, meta = self.plan(runs, want)
+        dev = self._upload(buf)
+        ctx = self.context(lay, dev, meta)
+        logits = self.model.forward(ctx, self.cache)
+        for s, n in zip(meta["slots"], meta["new_lens"]):
+            self.cache.commit(s, n)
+        return logits

@@ -1,0 +1,347 @@
+"""Python face of the CUDA kernels.
+
+Every function checks sizes, element types and devices on the host, then calls
+one launcher on the current CUDA stream.  There is no CPU implementation and no
+library fallback: a tensor that is not on a CUDA device, or a library that does
+not build, is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build, catalog
+
+PAGE = 64                      # tokens per cache page (GL_PAGE)
+F32, BF16 = 0, 1
+ACTIVATIONS = {"none": 0, None: 0, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "relu": 3}
+SAMPLE_WINDOW = 64             # tokens the repeat penalty looks back on (runtime.go:27)
+SAMPLE_KMAX = 1024
+
+_ERRORS = {
+    -1: "this combination of element types is not built",
+    -2: "a size the kernel does not take",
+    -3: "a pointer or stride is not aligned as the kernel requires",
+    -4: "the launch failed (cudaGetLastError)",
+    -5: "the kernel needs more shared memory than the device allows",
+    -6: "a CUDA driver entry point is missing or failed",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+
+
+def dtype_code(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return F32
+    if t == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {t} is not supported by the kernels (float32 and bfloat16 are)")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _addr(t: Optional[torch.Tensor]):
+    """Address for a structure field (None is a null pointer)."""
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: the kernels have no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, has {tuple(t.shape)}")
+
+
+def _lib(source: str, defines=()):
+    return build.load(source, tuple(defines))
+
+
+# ---------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0,
+          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = scale * table[tokens[t]] as float32."""
+    _need(table, "table")
+    _need(tokens, "tokens", torch.int32)
+    V, D = table.shape
+    T = tokens.numel()
+    if out is None:
+        out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    _need(out, "out", torch.float32, (T, D))
+    fn = _lib("rowwise.cu").gl_embed
+    _check(fn(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
+              c_int(T), c_int(D), c_int(V), c_float(scale), _stream()), "embed")
+    return out
+
+
+def norm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float,
+         out_dtype: torch.dtype, rms: bool = False, rows: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm (or RMSNorm) of float32 rows; ``rows`` picks rows of x."""
+    _need(x, "x", torch.float32)
+    D = x.shape[-1]
+    _need(gamma, "gamma", torch.float32, (D,))
+    if beta is not None:
+        _need(beta, "beta", torch.float32, (D,))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        R = rows.numel()
+    else:
+        R = x.numel() // D
+    if out is None:
+        out = torch.empty((R, D), dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype, (R, D))
+    fn = _lib("rowwise.cu").gl_norm
+    _check(fn(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), c_int(dtype_code(out_dtype)),
+              c_int(R), c_int(D), c_float(eps), c_int(1 if rms else 0), _stream()), "norm")
+    return out
+
+
+def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor):
+    """cos and sin of float32(pos) * inv_freq, each [T, half] float32."""
+    _need(pos, "pos", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    T, half = pos.numel(), inv_freq.numel()
+    cosv = torch.empty((T, half), dtype=torch.float32, device=pos.device)
+    sinv = torch.empty_like(cosv)
+    fn = _lib("qkv_cache.cu").gl_rope_table
+    _check(fn(_ptr(pos), _ptr(inv_freq), _ptr(cosv), _ptr(sinv), c_int(T), c_int(half), _stream()),
+           "rope_table")
+    return cosv, sinv
+
+
+class _QkvCacheArgs(Structure):
+    _fields_ = [("qkv", c_void_p), ("q_out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("cosv", c_void_p), ("sinv", c_void_p),
+                ("q_gamma", c_void_p), ("q_beta", c_void_p), ("k_gamma", c_void_p), ("k_beta", c_void_p),
+                ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("pages", c_void_p),
+                ("T", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("half", c_int),
+                ("max_pages", c_int), ("interleaved", c_int), ("norm_rms", c_int), ("write_kv", c_int),
+                ("eps", c_float), ("q_scale", c_float)]
+
+
+def qkv_to_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 tok_seq: torch.Tensor, tok_pos: torch.Tensor, pages: torch.Tensor,
+                 num_heads: int, num_kv_heads: int, head_dim: int, q_scale: float,
+                 cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                 interleaved: bool = False,
+                 q_norm=None, k_norm=None, norm_eps: float = 0.0, norm_rms: bool = False,
+                 write_kv: bool = True) -> None:
+    """Head norm, rotation and scale of projected rows; q to ``q_out``, k and v into cache pages.
+
+    qkv: [T, (nH + 2 nKV) * hd]; k_cache, v_cache: [pages, nKV, PAGE, hd];
+    pages: [B, max_pages] int32; q_norm / k_norm: (gamma, beta or None) or None.
+    """
+    _need(qkv, "qkv")
+    T = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(qkv, "qkv", shape=(T, width))
+    _need(q_out, "q_out", qkv.dtype, (T, num_heads * head_dim))
+    _need(k_cache, "k_cache")
+    _need(v_cache, "v_cache", k_cache.dtype, k_cache.shape)
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pages must be [*, {num_kv_heads}, {PAGE}, {head_dim}], are {tuple(k_cache.shape)}")
+    _need(tok_seq, "tok_seq", torch.int32, (T,))
+    _need(tok_pos, "tok_pos", torch.int32, (T,))
+    _need(pages, "pages", torch.int32)
+    half = 0
+    if cos is not None:
+        half = cos.shape[-1]
+        _need(cos, "cos", torch.float32, (T, half))
+        _need(sin, "sin", torch.float32, (T, half))
+        if 2 * half > head_dim:
+            raise KernelError(f"rotary dimension {2 * half} exceeds head size {head_dim}")
+    qg = qb = kg = kb = None
+    if q_norm is not None:
+        qg, qb = q_norm
+        kg, kb = k_norm
+        for n, t in (("q_norm.gamma", qg), ("k_norm.gamma", kg)):
+            _need(t, n, torch.float32, (head_dim,))
+        for n, t in (("q_norm.beta", qb), ("k_norm.beta", kb)):
+            if t is not None:
+                _need(t, n, torch.float32, (head_dim,))
+    a = _QkvCacheArgs(qkv.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                      _addr(cos), _addr(sin), _addr(qg), _addr(qb), _addr(kg), _addr(kb),
+                      tok_seq.data_ptr(), tok_pos.data_ptr(), pages.data_ptr(),
+                      T, num_heads, num_kv_heads, head_dim, half, pages.shape[-1],
+                      1 if interleaved else 0, 1 if norm_rms else 0, 1 if write_kv else 0,
+                      norm_eps, q_scale)
+    fn = _lib("qkv_cache.cu").gl_qkv_cache
+    _check(fn(byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+           "qkv_to_cache")
+
+
+class _AttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
+                ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("max_pages", c_int),
+                ("window", c_int), ("max_qlen", c_int), ("score_scale", c_float)]
+
+
+def _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+               num_heads, num_kv_heads, head_dim, window, max_qlen, score_scale) -> _AttnArgs:
+    T = q.shape[0]
+    _need(q, "q", shape=(T, num_heads * head_dim))
+    _need(out, "out", q.dtype, q.shape)
+    _need(k_cache, "k_cache")
+    _need(v_cache, "v_cache", k_cache.dtype, k_cache.shape)
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pages must be [*, {num_kv_heads}, {PAGE}, {head_dim}], are {tuple(k_cache.shape)}")
+    B = seq_qlen.numel()
+    for n, t in (("seq_qstart", seq_qstart), ("seq_qlen", seq_qlen), ("seq_ctx", seq_ctx)):
+        _need(t, n, torch.int32, (B,))
+    _need(pages, "pages", torch.int32)
+    if pages.shape[0] != B:
+        raise KernelError(f"pages has {pages.shape[0]} rows for {B} sequences")
+    if num_heads % num_kv_heads:
+        raise KernelError(f"{num_heads} heads are not a multiple of {num_kv_heads} key/value heads")
+    return _AttnArgs(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                     seq_qstart.data_ptr(), seq_qlen.data_ptr(), seq_ctx.data_ptr(), pages.data_ptr(),
+                     B, num_heads, num_kv_heads, head_dim, pages.shape[-1], window, max_qlen, score_scale)
+
+
+def attention_generic(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+                      num_heads: int, num_kv_heads: int, head_dim: int, max_qlen: int,
+                      window: int = 0, score_scale: float = 1.0) -> None:
+    """Causal attention of this step's queries over the paged cache, 32-bit arithmetic."""
+    if head_dim > 256:
+        raise KernelError(f"head size {head_dim} exceeds 256")
+    a = _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+                   num_heads, num_kv_heads, head_dim, window, max_qlen, score_scale)
+    fn = _lib("attention_generic.cu").gl_attention_generic
+    _check(fn(byref(a), c_int(dtype_code(q.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+           "attention_generic")
+
+
+def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads: int,
+              head_dim: int, window: int = 0) -> None:
+    """Attention of a step's queries over the cache with the fastest kernel for the step's
+    shape and element type.  ``ctx`` is the step's context (per-sequence starts, lengths,
+    cached lengths on the device, the longest query run on the host)."""
+    attention_generic(q, out, k_cache, v_cache, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_ctx, pages,
+                      num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)
+
+
+class _GemmArgs(Structure):
+    _fields_ = [("a", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("add0", c_void_p),
+                ("add1", c_void_p), ("out", c_void_p),
+                ("M", c_int), ("N", c_int), ("K", c_int), ("act", c_int)]
+
+
+def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
+    _need(a, "a")
+    _need(w, "w")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"a is [{M}, {K}] but w is {tuple(w.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (N,))
+    for n, t in (("add0", add0), ("add1", add1)):
+        if t is not None:
+            _need(t, n, torch.float32, (M, N))
+    _need(out, "out", shape=(M, N))
+    if act not in ACTIVATIONS:
+        raise KernelError(f"activation {act!r} unknown")
+    return _GemmArgs(a.data_ptr(), w.data_ptr(), _addr(bias), _addr(add0), _addr(add1), out.data_ptr(),
+                     M, N, K, ACTIVATIONS[act])
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
+              add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
+              out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(a · wᵀ + bias) + add0 + add1 on CUDA cores in 32-bit (any element type, any size)."""
+    if out is None:
+        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    g = _gemm_args(a, w, bias, act, add0, add1, out)
+    fn = _lib("gemm_simt.cu").gl_gemm_simt
+    _check(fn(byref(g), c_int(dtype_code(a.dtype)), c_int(dtype_code(w.dtype)),
+              c_int(dtype_code(out.dtype)), _stream()), "gemm_simt")
+    return out
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
+           add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(a · wᵀ + bias) + add0 + add1 with the fastest kernel that takes these
+    types and sizes.  float32 operands always run the 32-bit CUDA-core product."""
+    return gemm_simt(a, w, bias, act, add0, add1, out_dtype, out)
+
+
+class _SampleArgs(Structure):
+    _fields_ = [("logits", c_void_p), ("work", c_void_p), ("state_row", c_void_p), ("recent", c_void_p),
+                ("recent_n", c_void_p), ("rng", c_void_p), ("out", c_void_p),
+                ("B", c_int), ("V", c_int), ("top_k", c_int),
+                ("temperature", c_float), ("top_p", c_float), ("min_p", c_float),
+                ("repeat_penalty", c_float)]
+
+
+def check_sampler(temperature: float, top_k: int, top_p: float, min_p: float, vocab: int) -> None:
+    """Raise if the kernel does not take this combination of options."""
+    greedy = temperature < 1e-6 or top_k == 1
+    if greedy:
+        return
+    whole = not (0 < top_k < vocab)
+    if not whole and top_k > SAMPLE_KMAX:
+        raise KernelError(f"top_k {top_k} exceeds {SAMPLE_KMAX}")
+    if whole and (top_p < 1.0 or min_p > 0.0):
+        raise KernelError("top_p < 1 or min_p > 0 need 0 < top_k < vocabulary "
+                          f"(top_k up to {SAMPLE_KMAX}); the whole-vocabulary nucleus is not built")
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, recent: torch.Tensor, recent_n: torch.Tensor,
+           rng: torch.Tensor, out: torch.Tensor, temperature: float, top_k: int, top_p: float,
+           min_p: float, repeat_penalty: float, state_row: Optional[torch.Tensor] = None) -> None:
+    """One token per row of float32 logits [B, V] into ``out`` [B] int32.
+
+    recent [R, 64] int32 / recent_n [R] int32: each state row's window of recent tokens
+    (the choice is appended); rng [R] int64: xorshift64 states; state_row [B] int32 says
+    which state row a logits row uses (None: row b uses state b)."""
+    _need(logits, "logits", torch.float32)
+    B, V = logits.shape
+    _need(work, "work", torch.float32)
+    if work.numel() < B * V:
+        raise KernelError("sampling scratch is smaller than the logits")
+    R = recent_n.numel()
+    _need(recent, "recent", torch.int32, (R, SAMPLE_WINDOW))
+    _need(recent_n, "recent_n", torch.int32, (R,))
+    _need(rng, "rng", torch.int64, (R,))
+    _need(out, "out", torch.int32)
+    if out.numel() < B:
+        raise KernelError("out is smaller than the batch")
+    if state_row is not None:
+        _need(state_row, "state_row", torch.int32)
+        if state_row.numel() < B:
+            raise KernelError("state_row is smaller than the batch")
+    elif R < B:
+        raise KernelError(f"{R} sampler states for {B} rows")
+    check_sampler(temperature, top_k, top_p, min_p, V)
+    a = _SampleArgs(logits.data_ptr(), work.data_ptr(), _addr(state_row), recent.data_ptr(),
+                    recent_n.data_ptr(), rng.data_ptr(), out.data_ptr(), B, V, top_k,
+                    temperature, top_p, min_p, repeat_penalty)
+    _check(_lib("sampling.cu").gl_sample(byref(a), _stream()), "sample")
+
+
+def warm_up(head_dims=()) -> None:
+    """Compile (if needed) and load every library a model with these head sizes uses."""
+    for src, defines in catalog.all_libraries(head_dims):
+        _lib(src, defines)

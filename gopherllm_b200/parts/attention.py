@@ -1,0 +1,93 @@
+"""Softmax attention over the paged key/value cache."""
+from __future__ import annotations
+
+from typing import Dict, Sequence
+
+import torch
+
+from .. import ops
+from ..config.specs import MixerSpec
+from .base import KVRequest, Mixer, ParamSpec, build_norm, build_position, register_mixer
+
+
+class Attention(Mixer):
+    """q, k, v projections (one fused product, rows ordered Q, K, V as the
+    reference's fused matrix is, model.go:2222-2227), optional per-head norm of
+    q and k, position encoding, query scale, cache write, attention over the
+    cache, output projection.  Grouped-query attention when num_kv_heads <
+    num_heads (query head h reads group h / (nH/nKV), model.go:2828)."""
+
+    def __init__(self, spec: MixerSpec):
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if spec.head_dim > 256:
+            raise ValueError(f"head size {spec.head_dim} exceeds what the attention kernels take (256)")
+        self.spec = spec
+        self.position = build_position(spec.position)
+        self.q_norm = build_norm(spec.qk_norm) if spec.qk_norm else None
+        self.k_norm = build_norm(spec.qk_norm) if spec.qk_norm else None
+        self.w_qkv = self.b_qkv = self.w_out = self.b_out = None
+
+    # -- parameters -----------------------------------------------------
+    def parameters(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        p = {"q.weight": ParamSpec((q, s.hidden)), "k.weight": ParamSpec((kv, s.hidden)),
+             "v.weight": ParamSpec((kv, s.hidden)), "out.weight": ParamSpec((s.hidden, q))}
+        if s.bias:
+            p.update({"q.bias": ParamSpec((q,), "vector", "bias"),
+                      "k.bias": ParamSpec((kv,), "vector", "bias"),
+                      "v.bias": ParamSpec((kv,), "vector", "bias"),
+                      "out.bias": ParamSpec((s.hidden,), "vector", "bias")})
+        if self.q_norm is not None:
+            for name, n in (("q_norm", self.q_norm), ("k_norm", self.k_norm)):
+                for k, v in n.parameters().items():
+                    p[f"{name}.{k}"] = v
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        ws = [t["q.weight"], t["k.weight"], t["v.weight"]]
+        if len({w.dtype for w in ws}) > 1:           # mixed storage: widen to the widest
+            ws = [w.float() for w in ws]
+        self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        self.w_out = t["out.weight"]
+        if self.spec.bias:
+            self.b_qkv = torch.cat([t["q.bias"], t["k.bias"], t["v.bias"]]).contiguous()
+            self.b_out = t["out.bias"]
+        if self.q_norm is not None:
+            self.q_norm.load({k[len("q_norm."):]: v for k, v in t.items() if k.startswith("q_norm.")})
+            self.k_norm.load({k[len("k_norm."):]: v for k, v in t.items() if k.startswith("k_norm.")})
+
+    def cache_request(self):
+        s = self.spec
+        return KVRequest(s.num_kv_heads, s.head_dim, s.window)
+
+    # -- compute ----------------------------------------------------------
+    def forward(self, xn, ctx, cache, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+        s = self.spec
+        T = xn.shape[0]
+        qkv = ops.linear(xn, self.w_qkv, self.b_qkv, out_dtype=ctx.act_dtype)
+        q = torch.empty((T, s.num_heads * s.head_dim), dtype=ctx.act_dtype, device=xn.device)
+        tables = self.position.tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        pages = ctx.pages[cache.group]
+        qn = kn = None
+        eps, rms = 0.0, False
+        if self.q_norm is not None:
+            qn, kn = (self.q_norm.weight, self.q_norm.bias), (self.k_norm.weight, self.k_norm.bias)
+            eps, rms = s.qk_norm.eps, self.q_norm.rms
+        ops.qkv_to_cache(qkv, q, cache.k, cache.v, ctx.tok_seq, ctx.tok_pos, pages,
+                         s.num_heads, s.num_kv_heads, s.head_dim, s.q_scale, cos, sin,
+                         interleaved=s.position.interleaved, q_norm=qn, k_norm=kn,
+                         norm_eps=eps, norm_rms=rms, write_kv=cache.writes)
+        o = torch.empty_like(q)
+        ops.attention(q, o, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads,
+                      s.head_dim, window=s.window)
+        a0 = add[0] if len(add) > 0 else None
+        a1 = add[1] if len(add) > 1 else None
+        if len(add) > 2:
+            raise ValueError("at most two tensors can be added in the projection's epilogue")
+        return ops.linear(o, self.w_out, self.b_out, add0=a0, add1=a1, out=out)
+
+
+register_mixer("attention", Attention)

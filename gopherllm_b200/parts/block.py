@@ -1,0 +1,68 @@
+"""Arrangements of norm, mixer and feed-forward in one layer."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..config.specs import BlockSpec
+from .base import Block, ParamSpec, build_feed_forward, build_mixer, build_norm, register_block
+
+
+class _AssembledBlock(Block):
+    def __init__(self, spec: BlockSpec):
+        self.spec = spec
+        self.norm = build_norm(spec.norm)
+        self.norm2 = build_norm(spec.norm2) if spec.norm2 is not None else None
+        self.mixer = build_mixer(spec.mixer)
+        self.ffn = build_feed_forward(spec.ffn)
+
+    def _children(self):
+        yield "norm", self.norm
+        if self.norm2 is not None:
+            yield "norm2", self.norm2
+        yield "mixer", self.mixer
+        yield "ffn", self.ffn
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        """Keys are "<slot>/<parameter>": the slot names the child part."""
+        return {f"{slot}/{k}": v for slot, part in self._children() for k, v in part.parameters().items()}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for slot, part in self._children():
+            pre = slot + "/"
+            part.load({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)})
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+
+class ParallelBlock(_AssembledBlock):
+    """x ← x + ffn(n) + mixer(n), n = norm(x): one norm feeds both branches
+    (model.go:2738-2740) and both are added to the residual, the feed-forward
+    first (model.go:2812-2815)."""
+
+    def forward(self, x, ctx, cache):
+        xn = self.norm.forward(x, ctx.act_dtype)
+        a = torch.empty_like(x)
+        self.mixer.forward(xn, ctx, cache, (), a)
+        self.ffn.forward(xn, ctx, (x, a), x)
+        return x
+
+
+class SequentialBlock(_AssembledBlock):
+    """x ← x + mixer(norm(x)); x ← x + ffn(norm2(x)) (model.go:2806-2811)."""
+
+    def __init__(self, spec: BlockSpec):
+        if spec.norm2 is None:
+            raise ValueError("a sequential block needs norm2")
+        super().__init__(spec)
+
+    def forward(self, x, ctx, cache):
+        self.mixer.forward(self.norm.forward(x, ctx.act_dtype), ctx, cache, (x,), x)
+        self.ffn.forward(self.norm2.forward(x, ctx.act_dtype), ctx, (x,), x)
+        return x
+
+
+register_block("parallel", ParallelBlock)
+register_block("sequential", SequentialBlock)

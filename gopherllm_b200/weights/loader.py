@@ -1,0 +1,156 @@
+"""Weights by tensor name: checking a model folder against what the model's
+parts declare, loading, and the seeded random-weights mode.
+
+The reference looks tensors up by name in the file's table (model.go:2260-2266,
+2357-2473) and fails on the first problem ("missing tensor: %s",
+model.go:2360; "phi2 requires %d-element output.bias", model.go:1903).  Here all
+problems of a folder are collected into one error: missing tensors, tensors the
+model does not know, and wrong shapes.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+from typing import Callable, Dict, Iterator, List, Optional, Tuple
+
+import torch
+
+from ..parts.base import ParamSpec
+from .safetensors_io import TensorFile, index_folder, write_file
+
+STORAGE_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16,
+                  "bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}
+
+
+class WeightsError(ValueError):
+    """A model folder does not hold what the model needs."""
+
+    def __init__(self, folder: str, missing: List[str], unexpected: List[str], wrong: List[str]):
+        self.missing, self.unexpected, self.wrong = missing, unexpected, wrong
+        lines = [f"{folder}: the weights do not fit the model"]
+        if missing:
+            lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
+        if unexpected:
+            lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
+        if wrong:
+            lines.append(f"  wrong shapes or types ({len(wrong)}): " + "; ".join(wrong))
+        super().__init__("\n".join(lines))
+
+
+def tensor_table(model_parameters: Dict[str, ParamSpec], names) -> Dict[str, Tuple[str, ParamSpec]]:
+    """file tensor name -> (model parameter key, spec).  Keys are "embedding",
+    "final_norm/<p>", "head/<p>" and "layers/<i>/<slot>/<p>"."""
+    table: Dict[str, Tuple[str, ParamSpec]] = {}
+    for key, spec in model_parameters.items():
+        parts = key.split("/")
+        if parts[0] == "embedding":
+            name = names.embedding
+        elif parts[0] == "final_norm":
+            name = f"{names.final_norm}.{parts[1]}"
+        elif parts[0] == "head":
+            name = f"{names.head}.{parts[1]}"
+        elif parts[0] == "layers":
+            name = names.layer(int(parts[1]), parts[2], parts[3])
+        else:
+            raise KeyError(f"model parameter {key!r} has no tensor name")
+        if name in table:
+            raise KeyError(f"tensor name {name} is used by two parameters")
+        table[name] = (key, spec)
+    return table
+
+
+def resident_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
+    """The type a tensor is held in.  Integer tables: int32.  1-D tensors:
+    float32 (model.go:2519-2528).  Matrices: float32 in the 32-bit path; in the
+    bfloat16 path a matrix stored in bfloat16 stays so, one stored in 32-bit
+    stays 32-bit, other types widen to float32."""
+    if spec.kind == "table_int":
+        return torch.int32
+    if spec.kind == "vector" or compute == torch.float32:
+        return torch.float32
+    return torch.bfloat16 if stored == torch.bfloat16 else torch.float32
+
+
+def check_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], ignore: Tuple[str, ...] = ()):
+    """Compare the folder's tensor table with what the model declares."""
+    entries = index_folder(folder)
+    missing = sorted(n for n, (_, spec) in table.items() if n not in entries and not spec.optional)
+    unexpected = sorted(n for n in entries if n not in table and n not in ignore)
+    wrong = []
+    for n, (_, spec) in sorted(table.items()):
+        e = entries.get(n)
+        if e is None:
+            continue
+        if tuple(e.shape) != tuple(spec.shape):
+            wrong.append(f"{n} is {list(e.shape)}, the model wants {list(spec.shape)}")
+        elif spec.kind != "table_int" and e.dtype not in ("F32", "F16", "BF16", "F64"):
+            wrong.append(f"{n} is stored as {e.dtype}, not a floating-point type")
+    if missing or unexpected or wrong:
+        raise WeightsError(folder, missing, unexpected, wrong)
+    return entries
+
+
+def load_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], compute: torch.dtype, device,
+                ignore: Tuple[str, ...] = (), progress: Optional[Callable[[str], None]] = None
+                ) -> Tuple[Dict[str, torch.Tensor], int]:
+    """Tensors by model parameter key, on ``device``; and the bytes read."""
+    entries = check_folder(folder, table, ignore)
+    out: Dict[str, torch.Tensor] = {}
+    nbytes = 0
+    with TensorFile(entries) as tf:
+        for i, (name, (key, spec)) in enumerate(sorted(table.items())):
+            if name not in entries:          # optional and absent
+                out[key] = torch.zeros(spec.shape, dtype=resident_dtype(spec, torch.float32, compute), device=device)
+                continue
+            t = tf.get(name)
+            nbytes += t.numel() * t.element_size()
+            out[key] = t.to(device=device, dtype=resident_dtype(spec, t.dtype, compute)).contiguous()
+            if progress and i % 64 == 0:
+                progress(f"loaded {i + 1}/{len(table)} tensors")
+    return out, nbytes
+
+
+# ---------------------------------------------------------------------------
+# random weights
+# ---------------------------------------------------------------------------
+def _tensor_seed(seed: int, name: str) -> int:
+    h = hashlib.sha256(f"{int(seed)}:{name}".encode()).digest()
+    return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
+
+
+def random_tensors(table: Dict[str, Tuple[str, ParamSpec]], seed: int, sigma: float,
+                   storage: torch.dtype, device="cpu") -> Iterator[Tuple[str, torch.Tensor]]:
+    """(name, tensor) for every declared tensor, each from a generator seeded by
+    (seed, name) so values do not depend on the order of generation.  Matrices
+    N(0, sigma); biases and norm offsets N(0, 0.02); norm scales 1 + N(0, 0.02).
+    Drawn in float32 on ``device`` and rounded to ``storage``."""
+    for name, (_, spec) in sorted(table.items()):
+        if spec.kind == "table_int":
+            yield name, torch.zeros(spec.shape, dtype=torch.int32)
+            continue
+        g = torch.Generator(device=device)
+        g.manual_seed(_tensor_seed(seed, name))
+        z = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
+        if spec.init == "normal":
+            t = z * sigma
+        elif spec.init in ("bias", "beta"):
+            t = z * 0.02
+        elif spec.init == "gamma":
+            t = 1.0 + z * 0.02
+        elif spec.init == "zeros":
+            t = torch.zeros_like(z)
+        else:
+            raise ValueError(f"{name}: unknown initialisation {spec.init!r}")
+        yield name, t.to(storage).cpu()
+
+
+def write_model_folder(folder: str, config_dict: dict, table: Dict[str, Tuple[str, ParamSpec]],
+                       seed: int, sigma: float, storage: torch.dtype, device="cpu") -> None:
+    """config.json and model.safetensors of a random model."""
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(config_dict, f, indent=2, sort_keys=True)
+    write_file(os.path.join(folder, "model.safetensors"),
+               random_tensors(table, seed, sigma, storage, device),
+               metadata={"format": "pt", "seed": seed})

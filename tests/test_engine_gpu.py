@@ -1,0 +1,167 @@
+"""The engine against the plain implementation: every way of cutting the work."""
+import numpy as np
+import pytest
+import torch
+
+import plain_phi
+import tiny
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+_PLAIN = {}
+_MODELS = {}
+
+
+def plain_logits(name, tokens):
+    key = (name, tuple(tokens))
+    if key not in _PLAIN:
+        cfg, W = plain_phi.read_folder(tiny.folder(name))
+        _PLAIN[key] = plain_phi.phi_logits(tokens, W, cfg).numpy()
+    return _PLAIN[key]
+
+
+def model(name, dtype):
+    import gopherllm_b200 as gl
+    key = (name, dtype)
+    if key not in _MODELS:
+        _MODELS[key] = gl.load(tiny.folder(name), dtype=dtype, max_tokens=1024)
+    return _MODELS[key]
+
+
+def check(got, ref, dtype, what):
+    err, bound = tiny.close(got, ref, dtype)
+    assert err <= bound, f"{what}: max |diff| {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_prompt_every_position(name, dtype):
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(10)
+    m = model(name, dtype)
+    for n in (1, 7, 64, 65, cfg["max_position_embeddings"] - 1):
+        toks = tiny.prompt(rng, n, cfg["vocab_size"])
+        s = m.open_sequence()
+        got = m.step([(s, toks)], [list(range(n))]).cpu().numpy()
+        m.close_sequence(s)
+        check(got, plain_logits(name, toks), dtype, f"{name} whole n={n}")
+    m.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(name, dtype):
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(11)
+    m = model(name, dtype)
+    n = cfg["max_position_embeddings"] - 3
+    toks = tiny.prompt(rng, n, cfg["vocab_size"])
+    ref = plain_logits(name, toks)
+    s = m.open_sequence()
+    head = n - 32
+    got = [m.step([(s, toks[:head])], [list(range(head))]).cpu().numpy()]
+    for t in range(head, n):
+        got.append(m.step([(s, [toks[t]])], [[0]]).cpu().numpy())
+    m.close_sequence(s)
+    got = np.concatenate(got)
+    for t in range(n):      # find the first wrong place, not just the largest error
+        err, bound = tiny.close(got[t], ref[t], dtype)
+        assert err <= bound, f"{name} {dtype}: first wrong position {t} (prompt part ends at {head}): {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(name, dtype):
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(12)
+    m = model(name, dtype)
+    toks = tiny.prompt(rng, 6, cfg["vocab_size"])
+    ref = plain_logits(name, toks)
+    s = m.open_sequence()
+    for t in range(6):      # from the very first token, one at a time
+        got = m.step([(s, [toks[t]])], [[0]]).cpu().numpy()
+        check(got[0], ref[t], dtype, f"{name} position {t} decoded from an empty cache")
+    m.close_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_one_after_another(name, dtype):
+    """Prompts of unequal lengths in one step, then one token each; shorter requests end
+    earlier; a second batch reuses the slots and pages, one slot after a longer sequence."""
+    cfg = tiny.TINY[name][0]
+    V, P = cfg["vocab_size"], cfg["max_position_embeddings"]
+    rng = np.random.default_rng(13)
+    m = model(name, dtype)
+    cache = m.engine.cache
+    for lens, decs in (([P - 40, 5, 64, 17], [20, 3, 9, 1]), ([3, 65, 1], [30, 12, 5])):
+        seqs = [tiny.prompt(rng, a + d, V) for a, d in zip(lens, decs)]
+        refs = [plain_logits(name, s) for s in seqs]
+        slots = [m.open_sequence() for _ in seqs]
+        got = [[] for _ in seqs]
+        out = m.step([(slots[i], seqs[i][:lens[i]]) for i in range(len(seqs))],
+                     [list(range(lens[i])) for i in range(len(seqs))]).cpu().numpy()
+        o = 0
+        for i, a in enumerate(lens):
+            got[i].append(out[o:o + a])
+            o += a
+        live = list(range(len(seqs)))
+        for step in range(max(decs)):
+            live = [i for i in live if step < decs[i]]
+            out = m.step([(slots[i], [seqs[i][lens[i] + step]]) for i in live]).cpu().numpy()
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1])
+            for i in live:
+                if step + 1 == decs[i]:
+                    m.close_sequence(slots[i])      # ends earlier: its slot goes back now
+        for i in range(len(seqs)):
+            g = np.concatenate(got[i])
+            for t in range(len(seqs[i])):
+                err, bound = tiny.close(g[t], refs[i][t], dtype)
+                assert err <= bound, (f"{name} {dtype} batch {lens}: request {i} first wrong at position {t} "
+                                      f"(prompt {lens[i]}): {err:.3e} > {bound:.3e}")
+        cache.check()
+        assert cache.slots.held_count == 0 and all(g.pool.held_count == 0 for g in cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(dtype):
+    """A short prompt, then decoding up to the model's last position."""
+    name = "B"
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(14)
+    m = model(name, dtype)
+    n = cfg["max_position_embeddings"]
+    toks = tiny.prompt(rng, n, cfg["vocab_size"])
+    ref = plain_logits(name, toks)
+    s = m.open_sequence()
+    m.step([(s, toks[:4])], [[]])
+    for t in range(4, n):
+        got = m.step([(s, [toks[t]])]).cpu().numpy()
+        err, bound = tiny.close(got[0], ref[t], dtype)
+        assert err <= bound, f"{dtype}: first wrong position {t}: {err:.3e} > {bound:.3e}"
+    with pytest.raises(Exception):
+        m.step([(s, [1])])          # the sequence is full
+    m.close_sequence(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batch_composition_does_not_change_a_row(dtype):
+    name = "A"
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(15)
+    m = model(name, dtype)
+    a = tiny.prompt(rng, 33, cfg["vocab_size"])
+    others = [tiny.prompt(rng, k, cfg["vocab_size"]) for k in (90, 2, 64)]
+    s = m.open_sequence()
+    alone = m.step([(s, a)], [list(range(33))]).cpu().numpy()
+    m.close_sequence(s)
+    slots = [m.open_sequence() for _ in range(4)]
+    runs = [(slots[0], others[0]), (slots[1], a), (slots[2], others[1]), (slots[3], others[2])]
+    out = m.step(runs, [[], list(range(33)), [], []]).cpu().numpy()
+    for sl in slots:
+        m.close_sequence(sl)
+    if dtype == "float32":
+        assert np.array_equal(alone, out), "a 32-bit row changed with the batch around it"
+    else:
+        check(out, alone, dtype, "row in a batch vs alone")
