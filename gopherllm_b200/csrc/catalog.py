@@ -4,10 +4,11 @@ from __future__ import annotations
 from typing import Iterable, Iterator, Tuple
 
 # libraries that do not depend on a model's sizes
-GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu", "sampling.cu")
+GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu", "gemm_skinny.cu",
+           "sampling.cu")
 
 # libraries compiled once per head size (GL_HEAD_DIM)
-PER_HEAD_DIM: Tuple[str, ...] = ()
+PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu",)
 
 
 def head_dim_defines(head_dim: int) -> Tuple[str, ...]:

@@ -232,11 +232,80 @@ def attention_generic(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, p
            "attention_generic")
 
 
+class _DecodeArgs(Structure):
+    _fields_ = [("q", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("seq_ctx", c_void_p), ("pages", c_void_p), ("part_o", c_void_p), ("part_ml", c_void_p),
+                ("B", c_int), ("nH", c_int), ("nKV", c_int), ("max_pages", c_int), ("window", c_int),
+                ("splits", c_int)]
+
+
+DECODE_MAX_GROUP = 8      # query heads per key/value head the decode kernel takes
+_SM_COUNT = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def decode_splits(batch: int, num_kv_heads: int, max_len: int, device) -> int:
+    """How many blocks share one (sequence, key/value head): enough to put about four
+    blocks on every SM, never more than the longest sequence has pages."""
+    pages = max(1, -(-max_len // PAGE))
+    want = -(-4 * sm_count(device) // max(1, batch * num_kv_heads))
+    return max(1, min(want, pages, 64))
+
+
+def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, num_kv_heads: int,
+                     head_dim: int, splits: int, window: int = 0,
+                     scratch: Optional[torch.Tensor] = None) -> None:
+    """One query per sequence (row b of q is sequence b) over the bfloat16 cache.
+    ``scratch`` (float32, at least B*nH*splits*(hd+2) elements) holds the splits' partial
+    results; it is allocated when not given."""
+    B = q.shape[0]
+    _need(q, "q", torch.bfloat16, (B, num_heads * head_dim))
+    _need(out, "out", torch.bfloat16, q.shape)
+    _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pages must be [*, {num_kv_heads}, {PAGE}, {head_dim}], are {tuple(k_cache.shape)}")
+    _need(seq_ctx, "seq_ctx", torch.int32, (B,))
+    _need(pages, "pages", torch.int32)
+    if pages.shape[0] != B:
+        raise KernelError(f"pages has {pages.shape[0]} rows for {B} sequences")
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise KernelError(f"decode attention takes head sizes 16..256 in steps of 16, not {head_dim}")
+    if num_heads % num_kv_heads or num_heads // num_kv_heads > DECODE_MAX_GROUP:
+        raise KernelError(f"decode attention takes up to {DECODE_MAX_GROUP} query heads per key/value head")
+    lib = _lib("attention_decode.cu", catalog.head_dim_defines(head_dim))
+    part_o = part_ml = None
+    if splits > 1:
+        n_o, n_ml = B * num_heads * splits * head_dim, B * num_heads * splits * 2
+        if scratch is None:
+            scratch = torch.empty(n_o + n_ml, dtype=torch.float32, device=q.device)
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < n_o + n_ml:
+            raise KernelError("decode attention scratch is too small")
+        part_o, part_ml = scratch.data_ptr(), scratch.data_ptr() + 4 * n_o
+    a = _DecodeArgs(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                    seq_ctx.data_ptr(), pages.data_ptr(), part_o, part_ml,
+                    B, num_heads, num_kv_heads, pages.shape[-1], window, splits)
+    _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode")
+
+
 def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads: int,
               head_dim: int, window: int = 0) -> None:
     """Attention of a step's queries over the cache with the fastest kernel for the step's
     shape and element type.  ``ctx`` is the step's context (per-sequence starts, lengths,
-    cached lengths on the device, the longest query run on the host)."""
+    cached lengths on the device; the longest query run and sequence on the host)."""
+    if (ctx.is_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+            and head_dim % 16 == 0 and num_heads // num_kv_heads <= DECODE_MAX_GROUP):
+        splits = decode_splits(ctx.n_seqs, num_kv_heads, ctx.max_len, q.device)
+        attention_decode(q, out, k_cache, v_cache, ctx.seq_ctx, pages, num_heads, num_kv_heads,
+                         head_dim, splits, window)
+        return
     attention_generic(q, out, k_cache, v_cache, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_ctx, pages,
                       num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)
 
@@ -279,11 +348,34 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     return out
 
 
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
+                add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+                split_k: int = 0) -> torch.Tensor:
+    """The weight-streaming product for up to 64 rows of bfloat16 activations (K a multiple of 8)."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    if out is None:
+        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    g = _gemm_args(a, w, bias, act, add0, add1, out)
+    if a.shape[0] > SKINNY_MAX_ROWS or a.shape[1] % 8:
+        raise KernelError(f"gemm_skinny takes up to {SKINNY_MAX_ROWS} rows and K a multiple of 8")
+    fn = _lib("gemm_skinny.cu").gl_gemm_skinny
+    _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_skinny")
+    return out
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
            add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = act(a · wᵀ + bias) + add0 + add1 with the fastest kernel that takes these
     types and sizes.  float32 operands always run the 32-bit CUDA-core product."""
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0:
+        if a.shape[0] <= SKINNY_MAX_ROWS:
+            return gemm_skinny(a, w, bias, act, add0, add1, out_dtype, out)
     return gemm_simt(a, w, bias, act, add0, add1, out_dtype, out)
 
 

@@ -1,0 +1,361 @@
+"""Each kernel alone against a plain reference, at sizes other than the models'."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_phi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = 64
+
+
+def ops():
+    from gopherllm_b200 import ops as o
+    return o
+
+
+def gelu_ref(x, act):
+    if act in (None, "none"):
+        return x
+    return plain_phi.ACTIVATIONS[act](x)
+
+
+def ref_linear(a, w, bias, act, add0, add1):
+    v = a.double() @ w.double().T
+    if bias is not None:
+        v = v + bias.double()
+    v = gelu_ref(v, act)
+    for t in (add0, add1):
+        if t is not None:
+            v = v + t.double()
+    return v
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 77, 33), (130, 200, 96), (64, 64, 16), (3, 1000, 416)])
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16)])
+def test_gemm_simt(M, N, K, adt, wdt):
+    o = ops()
+    a, w = rnd(M, K, dtype=adt), rnd(N, K, dtype=wdt, seed=1)
+    bias, add0, add1 = rnd(N, seed=2), rnd(M, N, seed=3), rnd(M, N, seed=4)
+    for act in (None, "gelu_new", "gelu", "relu"):
+        got = o.gemm_simt(a, w, bias, act, add0, add1, out_dtype=torch.float32)
+        ref = ref_linear(a, w, bias, act, add0, add1)
+        assert (got.double() - ref).abs().max() <= 2e-5 * max(1.0, ref.abs().max().item())
+    got = o.gemm_simt(a, w, out_dtype=torch.bfloat16)
+    ref = ref_linear(a, w, None, None, None, None)
+    assert (got.double() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item())
+    # in place on the residual stream
+    x = add0.clone()
+    o.gemm_simt(a, w, bias, None, x, add1, out=x)
+    assert (x.double() - ref_linear(a, w, bias, None, add0, add1)).abs().max() <= 2e-5 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(40, 160), (1000, 200), (2560, 2560), (130, 4104)])
+def test_gemm_skinny(M, N, K):
+    o = ops()
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    bias, add0, add1 = rnd(N, seed=2), rnd(M, N, seed=3), rnd(M, N, seed=4)
+    for split in (0, 1, 2, 4, 8):
+        for act in (None, "gelu_new"):
+            got = o.gemm_skinny(a, w, bias, act, add0, add1, out_dtype=torch.float32, split_k=split)
+            ref = ref_linear(a, w, bias, act, add0, add1)
+            err = (got.double() - ref).abs().max().item()
+            assert err <= 3e-5 * max(1.0, ref.abs().max().item()), (split, act, err)
+    got = o.gemm_skinny(a, w, bias, "gelu", out_dtype=torch.bfloat16)
+    ref = ref_linear(a, w, bias, "gelu", None, None)
+    assert (got.double() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item())
+    with pytest.raises(Exception):
+        o.gemm_skinny(rnd(65, K, dtype=torch.bfloat16), w)
+
+
+def test_gemm_skinny_one_weight_stands_out():
+    """A single large weight far along K must reach exactly one output."""
+    o = ops()
+    M, N, K = 8, 192, 2048
+    a = torch.ones(M, K, dtype=torch.bfloat16, device=DEV)
+    for (n, k) in [(0, 0), (191, 2047), (77, 1029), (64, 31), (63, 32)]:
+        w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
+        w[n, k] = 3.0
+        for split in (1, 2, 4, 8):
+            got = o.gemm_skinny(a, w, out_dtype=torch.float32, split_k=split)
+            want = torch.zeros(M, N, device=DEV)
+            want[:, n] = 3.0
+            assert torch.equal(got, want), (n, k, split)
+
+
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("D", [5, 64, 160, 2560, 3000])
+def test_norm_and_embed(D):
+    o = ops()
+    x = rnd(11, D, scale=3.0) + 0.7
+    g, b = rnd(D, seed=1) + 1.0, rnd(D, seed=2)
+    for eps in (1e-5, 1e-6):
+        ref = plain_phi.layer_norm(x.double().cpu(), g.double().cpu(), b.double().cpu(), eps)
+        got = o.norm(x, g, b, eps, torch.float32)
+        assert (got.double().cpu() - ref).abs().max() <= 1e-5 * max(1.0, ref.abs().max().item())
+        rows = torch.tensor([10, 0, 3, 3], dtype=torch.int32, device=DEV)
+        got = o.norm(x, g, b, eps, torch.bfloat16, rows=rows)
+        assert (got.double().cpu() - ref[[10, 0, 3, 3]]).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item())
+        xr = x.double().cpu()
+        rms = xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + eps) * g.double().cpu()
+        got = o.norm(x, g, None, eps, torch.float32, rms=True)
+        assert (got.double().cpu() - rms).abs().max() <= 1e-5 * max(1.0, rms.abs().max().item())
+    for dt in (torch.float32, torch.bfloat16):
+        table = rnd(37, D, dtype=dt, seed=5)
+        toks = torch.tensor([36, 0, 5, 5, 17], dtype=torch.int32, device=DEV)
+        assert torch.equal(o.embed(table, toks), table[toks.long()].float())
+        assert torch.equal(o.embed(table, toks, scale=2.0), table[toks.long()].float() * 2.0)
+
+
+# --------------------------------------------------------------------------
+def make_cache(k, v, lens, dtype, seed=0, spare=5):
+    """Dense k, v [B, L, nKV, hd] -> paged cache with a shuffled page table."""
+    B, L, nKV, hd = k.shape
+    per = -(-L // PAGE)
+    n_pages = B * per + spare
+    perm = np.random.default_rng(seed).permutation(n_pages)
+    table = torch.zeros(B, per + 2, dtype=torch.int32)
+    kc = torch.full((n_pages, nKV, PAGE, hd), float("nan"), dtype=dtype, device=DEV)
+    vc = torch.full((n_pages, nKV, PAGE, hd), float("nan"), dtype=dtype, device=DEV)
+    c = 0
+    for b in range(B):
+        for p in range(-(-int(lens[b]) // PAGE)):
+            page = int(perm[c]); c += 1
+            table[b, p] = page
+            n = min(PAGE, int(lens[b]) - p * PAGE)
+            kc[page, :, :n] = k[b, p * PAGE:p * PAGE + n].transpose(0, 1).to(dtype)
+            vc[page, :, :n] = v[b, p * PAGE:p * PAGE + n].transpose(0, 1).to(dtype)
+    return kc, vc, table.to(DEV)
+
+
+def ref_attention(q, k, v, ctx, qlen, window):
+    """q [qlen, nH, hd] at positions ctx..ctx+qlen-1 over k, v [ctx+qlen, nKV, hd] (float64)."""
+    nH, nKV = q.shape[1], k.shape[1]
+    out = torch.zeros_like(q)
+    for h in range(nH):
+        g = h // (nH // nKV)
+        for i in range(qlen):
+            p = ctx + i
+            lo = max(0, p - window + 1) if window > 0 else 0
+            s = k[lo:p + 1, g] @ q[i, h]
+            w = torch.softmax(s, 0)
+            out[i, h] = (w[:, None] * v[lo:p + 1, g]).sum(0)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nH,nKV,hd", [(3, 3, 16), (4, 2, 80), (6, 1, 48), (2, 2, 256), (5, 5, 40)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_generic(dtype, nH, nKV, hd, window):
+    o = ops()
+    ctxs, qlens = [0, 130, 63, 5], [70, 1, 66, 9]
+    B, L = len(ctxs), max(c + q for c, q in zip(ctxs, qlens))
+    k = rnd(B, L, nKV, hd, seed=1).to(dtype).float()
+    v = rnd(B, L, nKV, hd, seed=2).to(dtype).float()
+    lens = [c + q for c, q in zip(ctxs, qlens)]
+    kc, vc, table = make_cache(k, v, lens, dtype)
+    T = sum(qlens)
+    q = (rnd(T, nH, hd, seed=3) / math.sqrt(hd)).to(dtype)
+    out = torch.empty(T, nH * hd, dtype=dtype, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    starts = np.concatenate([[0], np.cumsum(qlens)[:-1]]).tolist()
+    o.attention_generic(q.reshape(T, nH * hd), out, kc, vc, i32(starts), i32(qlens), i32(ctxs), table,
+                        nH, nKV, hd, max(qlens), window)
+    tol = 2e-5 if dtype == torch.float32 else 2 ** -7
+    for b in range(B):
+        ref = ref_attention(q[starts[b]:starts[b] + qlens[b]].double().cpu(), k[b, :lens[b]].double().cpu(),
+                            v[b, :lens[b]].double().cpu(), ctxs[b], qlens[b], window)
+        got = out[starts[b]:starts[b] + qlens[b]].reshape(qlens[b], nH, hd).double().cpu()
+        assert torch.isfinite(got).all()
+        assert (got - ref).abs().max() <= tol * max(1.0, ref.abs().max().item()), (b,)
+
+
+@pytest.mark.parametrize("nH,nKV,hd", [(4, 4, 16), (4, 2, 80), (6, 2, 48), (8, 1, 64), (2, 2, 256), (3, 3, 32)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode(nH, nKV, hd, window):
+    o = ops()
+    ctxs = [0, 63, 64, 700, 1, 333]
+    B, L = len(ctxs), max(ctxs) + 1
+    dtype = torch.bfloat16
+    k = rnd(B, L, nKV, hd, seed=1).to(dtype).float()
+    v = rnd(B, L, nKV, hd, seed=2).to(dtype).float()
+    lens = [c + 1 for c in ctxs]
+    kc, vc, table = make_cache(k, v, lens, dtype, seed=3)
+    q = (rnd(B, nH, hd, seed=3) / math.sqrt(hd)).to(dtype)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    for splits in (1, 2, 5, 16):
+        out = torch.empty(B, nH * hd, dtype=dtype, device=DEV)
+        o.attention_decode(q.reshape(B, nH * hd), out, kc, vc, i32(ctxs), table, nH, nKV, hd, splits, window)
+        for b in range(B):
+            ref = ref_attention(q[b:b + 1].double().cpu(), k[b, :lens[b]].double().cpu(),
+                                v[b, :lens[b]].double().cpu(), ctxs[b], 1, window)
+            got = out[b].reshape(1, nH, hd).double().cpu()
+            assert torch.isfinite(got).all()
+            assert (got - ref).abs().max() <= 2 ** -7 * max(1.0, ref.abs().max().item()), (b, splits)
+
+
+@pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode"])
+def test_attention_far_key_and_window_edge(kernel):
+    """One key among hundreds carries the whole weight: its value must come back.  With a
+    window the key at the window's edge is seen and the one before it is not."""
+    o = ops()
+    nH = nKV = 2
+    hd, L = 32, 600
+    dtype = torch.float32 if kernel == "generic32" else torch.bfloat16
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    for far, window, seen in [(3, 0, True), (64, 0, True), (599 - 99, 100, True), (599 - 100, 100, False),
+                              (599, 1, True), (598, 1, False), (0, 600, True), (0, 599, False)]:
+        k = torch.zeros(1, L, nKV, hd)
+        v = rnd(1, L, nKV, hd, seed=9).cpu()
+        k[0, far, :, 0] = 50.0                       # score 50 for this key, 0 for all others
+        q = torch.zeros(1, nH, hd)
+        q[..., 0] = 1.0
+        kc, vc, table = make_cache(k.to(DEV), v.to(DEV), [L], dtype, seed=far)
+        out = torch.empty(1, nH * hd, dtype=dtype, device=DEV)
+        qd = q.reshape(1, nH * hd).to(dtype).to(DEV)
+        if kernel == "decode":
+            o.attention_decode(qd, out, kc, vc, i32([L - 1]), table, nH, nKV, hd, 3, window)
+        else:
+            o.attention_generic(qd, out, kc, vc, i32([0]), i32([1]), i32([L - 1]), table, nH, nKV, hd, 1, window)
+        got = out.reshape(nH, hd).float().cpu()
+        want = v[0, far].to(dtype).float()
+        hit = (got - want).abs().max().item() < 0.02
+        assert hit == seen, (far, window, seen, (got - want).abs().max().item())
+
+
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nH,nKV,hd,rot", [(4, 4, 16, 8), (6, 2, 48, 24), (2, 2, 80, 32), (3, 1, 32, 0), (2, 2, 64, 64)])
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_qkv_to_cache(dtype, nH, nKV, hd, rot, qk_norm):
+    o = ops()
+    ctxs, qlens = [0, 100, 63], [66, 1, 2]
+    B, T = len(ctxs), sum(qlens)
+    theta, eps, scale = 500000.0, 1e-6, 1.0 / math.sqrt(hd)
+    tok_seq = np.repeat(np.arange(B), qlens)
+    tok_pos = np.concatenate([np.arange(c, c + n) for c, n in zip(ctxs, qlens)])
+    qkv = rnd(T, (nH + 2 * nKV) * hd, seed=4).to(dtype)
+    per = 3
+    table = torch.tensor(np.random.default_rng(1).permutation(B * per).reshape(B, per), dtype=torch.int32, device=DEV)
+    kc = torch.zeros(B * per, nKV, PAGE, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    i32 = lambda x: torch.tensor(np.asarray(x), dtype=torch.int32, device=DEV)
+    cos = sin = None
+    if rot:
+        from gopherllm_b200.parts.position import rope_inverse_frequencies
+        inv = rope_inverse_frequencies(rot, theta)
+        assert np.array_equal(inv, plain_phi.rope_inv_freq(rot, theta))
+        cos, sin = o.rope_table(i32(tok_pos), torch.from_numpy(inv).to(DEV))
+        rs, rc = plain_phi.rope_tables(tok_pos, rot, theta)
+        assert (cos.cpu() - rc).abs().max() <= 2e-7 and (sin.cpu() - rs).abs().max() <= 2e-7
+    norms = None
+    if qk_norm:
+        norms = [(rnd(hd, seed=5) + 1.0, rnd(hd, seed=6)), (rnd(hd, seed=7) + 1.0, rnd(hd, seed=8))]
+    q_out = torch.empty(T, nH * hd, dtype=dtype, device=DEV)
+    o.qkv_to_cache(qkv, q_out, kc, vc, i32(tok_seq), i32(tok_pos), table, nH, nKV, hd, scale, cos, sin,
+                   q_norm=norms[0] if norms else None, k_norm=norms[1] if norms else None, norm_eps=eps)
+    x = qkv.double().cpu().reshape(T, nH + 2 * nKV, hd)
+    q, k, v = x[:, :nH], x[:, nH:nH + nKV], x[:, nH + nKV:]
+    if qk_norm:
+        q = plain_phi.layer_norm(q, norms[0][0].double().cpu(), norms[0][1].double().cpu(), eps)
+        k = plain_phi.layer_norm(k, norms[1][0].double().cpu(), norms[1][1].double().cpu(), eps)
+    if rot:
+        rs, rc = plain_phi.rope_tables(tok_pos, rot, theta)
+        q, k = plain_phi.apply_rope(q, rs, rc, rot), plain_phi.apply_rope(k, rs, rc, rot)
+    q = q * scale
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    assert (q_out.double().cpu().reshape(T, nH, hd) - q).abs().max() <= tol * max(1.0, q.abs().max().item())
+    for t in range(T):
+        page = int(table[tok_seq[t], tok_pos[t] // PAGE])
+        gk = kc[page, :, tok_pos[t] % PAGE].double().cpu()
+        gv = vc[page, :, tok_pos[t] % PAGE].double().cpu()
+        assert (gk - k[t]).abs().max() <= tol * max(1.0, k.abs().max().item()), t
+        assert torch.equal(gv, v[t].to(dtype).double()), t
+    if rot and rot < hd and not qk_norm:       # dims past the rotary part pass through untouched
+        want = (x[:, :nH, rot:].float() * torch.tensor(scale, dtype=torch.float32)).to(dtype)
+        assert torch.equal(q_out.reshape(T, nH, hd)[..., rot:].cpu(), want)
+        got = torch.stack([kc[int(table[tok_seq[t], tok_pos[t] // PAGE]), :, tok_pos[t] % PAGE, rot:] for t in range(T)])
+        assert torch.equal(got.double().cpu(), x[:, nH:nH + nKV, rot:].to(dtype).double())
+    written = sum(qlens) * nKV * hd
+    assert int((kc != 0).sum()) <= written      # nothing outside the steps' positions was touched
+
+
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("V", [50, 1000, 51200])
+def test_sampling_matches_plain(V):
+    o = ops()
+    B = 5
+    rng = np.random.default_rng(V)
+    logits = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+    logits[1, 7] = np.nan
+    logits[2, 3] = np.inf
+    logits[3, : V // 2] = logits[3, V // 2 - 1]          # many equal values
+    recents = [list(rng.integers(0, V, size=n)) for n in (0, 5, 64, 64, 30)]
+    recents[2][5] = recents[2][9]                        # a token twice in the window
+    cases = [dict(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.3),
+             dict(temperature=0.7, top_k=40, top_p=0.9, min_p=0.0, repeat_penalty=1.1),
+             dict(temperature=0.95, top_k=7, top_p=0.95, min_p=0.05, repeat_penalty=1.05),
+             dict(temperature=1.5, top_k=1, top_p=0.9, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=0.8, top_k=33, top_p=1.0, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=0.8, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=1.0, top_k=V + 5, top_p=1.0, min_p=0.0, repeat_penalty=1.2)]
+    for ci, c in enumerate(cases):
+        if c["top_k"] > 0 and c["top_k"] >= V and (c["top_p"] < 1 or c["min_p"] > 0):
+            continue
+        dl = torch.from_numpy(logits).to(DEV)
+        work = torch.empty(B, V, device=DEV)
+        recent = torch.zeros(B, 64, dtype=torch.int32)
+        for i, r in enumerate(recents):
+            recent[i, :len(r)] = torch.tensor(r, dtype=torch.int32)
+        recent = recent.to(DEV)
+        recent_n = torch.tensor([len(r) for r in recents], dtype=torch.int32, device=DEV)
+        seeds = [11 + ci, 0xDEADBEEFCAFE1337, 3, 2 ** 63 + 5, 99]
+        rng_state = torch.tensor([s - 2 ** 64 if s >= 2 ** 63 else s for s in seeds], dtype=torch.int64, device=DEV)
+        out = torch.zeros(B, dtype=torch.int32, device=DEV)
+        draws = 3
+        got = []
+        for _ in range(draws):
+            o.sample(dl, work, recent, recent_n, rng_state, out, **c)
+            got.append(out.cpu().tolist())
+        assert torch.equal(dl.cpu().nan_to_num(0, 0, 0), torch.from_numpy(logits).nan_to_num(0, 0, 0)), "logits were modified"
+        for i in range(B):
+            r = plain_phi.Rng(seeds[i])
+            rec = list(recents[i])
+            for d in range(draws):
+                state_before = r.state
+                want = plain_phi.sample(logits[i], c["temperature"], c["top_k"], c["top_p"], c["min_p"],
+                                        c["repeat_penalty"], r, rec)
+                whole_row = c["temperature"] >= 1e-6 and not (0 < c["top_k"] < V)
+                if whole_row and got[d][i] != want:
+                    # The whole-row draw walks a running 32-bit sum of V weights; the plain loop adds
+                    # them one by one, the kernel by a parallel scan.  Two such sums of n terms with
+                    # total 1 differ by at most n * 2^-24, so the draw u may fall on either side of a
+                    # boundary that close: the kernel's token must hold u within that distance.
+                    u = float(plain_phi.Rng(state_before).next_f32())
+                    lg = logits[i].astype(np.float64).copy()
+                    lg[~np.isfinite(lg)] = -np.inf
+                    pen = np.float64(np.float32(c["repeat_penalty"]))
+                    for tok in rec:
+                        if lg[tok] > -np.inf and pen != 1:
+                            lg[tok] = lg[tok] / pen if lg[tok] > 0 else lg[tok] * pen
+                    wts = np.exp((lg - lg.max()) / np.float64(np.float32(c["temperature"])))
+                    cdf = np.cumsum(wts / wts.sum())
+                    g_ = got[d][i]
+                    slack = V * 2.0 ** -24
+                    lo_edge = cdf[g_ - 1] if g_ > 0 else 0.0
+                    assert lo_edge - slack <= u <= cdf[g_] + slack, (ci, i, d, g_, want, u, lo_edge, cdf[g_])
+                    want = g_
+                assert got[d][i] == want, (ci, i, d, got[d][i], want)
+                rec = (rec + [want])[-64:]
