@@ -1,0 +1,228 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Phi-2 sized model with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L]
+
+Prints one JSON line.  ``value`` is decoded tokens a second at the given batch and
+context, timed on the device over K decode steps that run back to back without the
+host (each step feeds the tokens the step before chose); ``e2e`` is the same work
+through the Python entry point ``Model.generate``, with host token lists in and out,
+every step copying its descriptor from pinned host memory and reading the chosen
+tokens back.  ``prefill`` is one prompt of 2,048 tokens; ``points`` are decode rates at
+batch 1 and 64; ``roofline`` relates the decode step to the bytes it has to read.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Phi-2 sizes: the layer sizes of the benchmark configuration
+PHI2 = dict(architectures=["PhiForCausalLM"], model_type="phi", num_hidden_layers=32, hidden_size=2560,
+            num_attention_heads=32, num_key_value_heads=32, intermediate_size=10240, vocab_size=51200,
+            partial_rotary_factor=0.4, rope_theta=10000.0, layer_norm_eps=1e-5, hidden_act="gelu_new",
+            qk_layernorm=False, tie_word_embeddings=False, max_position_embeddings=2048,
+            initializer_range=0.02, torch_dtype="bfloat16")
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048, help="positions each sequence holds when the timed steps end")
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="leave out prefill, batch 1 and batch 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "SimonWaldherr/GopherLLM is a Go module (no setup.py/pyproject.toml; pip reports 'not "
+                          "installable') and no Go toolchain exists offline, so it cannot be built or run here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for {args.gpus})")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+    import gopherllm_b200 as gl
+    from gopherllm_b200 import ops
+    from gopherllm_b200.sampling.sampler import DeviceSampler, SamplerConfig, request_seed
+
+    pk, pk_src = peaks()
+    cfg = dict(PHI2)
+    layers_full = cfg["num_hidden_layers"]
+    layers = args.layers or layers_full
+    K, W, B, C = args.steps, args.warmup, args.batch, args.context
+    max_b = B if args.skip_points else max(B, 64)
+    model = gl.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max_b * C, layers=layers)
+    eng = model.engine
+    spec = model.spec
+    rng = np.random.default_rng(4)
+    V = spec.vocab
+    greedy = SamplerConfig.greedy()
+    weight_bytes = sum(t.numel() * t.element_size() for t in eng.model._all_tensors()
+                       if t is not None and t.dim() == 2) - eng.model.embedding.numel() * eng.model.embedding.element_size()
+    kv_per_pos = eng.cache.bytes_per_position()
+
+    def decode_rate(batch, steps, warmup, context):
+        """tokens a second of `steps` on-device decode steps ending at `context` positions."""
+        prompt_len = context - steps - warmup - 1
+        prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(batch)]
+        slots = [eng.open() for _ in range(batch)]
+        sampler = DeviceSampler(greedy, [request_seed(5, i) for i in range(batch)], prompts, V, eng.device)
+        for i in range(0, batch, 8):                       # fill the cache, 8 prompts a step
+            logits = eng.step([(slots[j], prompts[j]) for j in range(i, min(batch, i + 8))])
+        first = [int(t) for t in rng.integers(0, V, size=batch)]
+        eng.decode_loop(slots, first, 1, sampler)          # captures the step
+        ops.LAUNCHES = 0
+        toks = eng.decode_loop(slots, first, warmup, sampler)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        toks = eng.decode_loop(slots, toks[-1].tolist(), steps, sampler)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        ctx_mid = context - 1 - steps / 2.0
+        for s in slots:
+            eng.close(s)
+        return batch * steps / (ms / 1e3), ms / steps, ctx_mid
+
+    clocks = ClockSampler()
+    clocks.start()
+    value, ms_step, ctx_mid = decode_rate(B, K, W, C)
+    clock_info = clocks.stop()
+    launches_per_step = eng.launches_per_loop_step.get(B, 0)
+
+    # the same work through the Python entry point: host tokens in, host tokens out
+    prompt_len = C - K - W - 1
+    prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(B)]
+    model.generate(prompts[:B], max_tokens=4, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                   stop_tokens=(), seed=5)                 # warm-up: captures the decode step for this batch
+    res = model.generate(prompts, max_tokens=K + W, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                         stop_tokens=(), seed=5)
+    dec_s = max(r.stats.decode_time for r in res)
+    e2e_value = sum(r.stats.generated_tokens - 1 for r in res) / dec_s
+    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.h2d_bytes_last + 4 * 0,
+           "d2h_bytes_per_step": 4 * B}
+
+    step_bytes = weight_bytes + B * ctx_mid * kv_per_pos
+    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8, context 2048 (Phi-2 sizes, bf16)" if (B, C) == (8, 2048)
+                  else f"decode tok/s at batch {B}, context {C} (Phi-2 sizes, bf16)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, token ids uniform in [0,51200)",
+        "config": {"model": "Phi-2 sizes (PhiForCausalLM)", "layers": layers, "layers_of_model": layers_full,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "rotary_dim": int(cfg["partial_rotary_factor"] * 80), "global_batch": B, "seq_len": C,
+                   "context_at_timed_steps": f"{C - K - 1}..{C - 1}", "parallelism": "single GPU",
+                   "sampling": "greedy", "l2": "each step reads weights and cache far larger than L2 (126 MB)",
+                   "peaks": pk_src},
+        "clocks": clock_info, "e2e": e2e, "gpu_launches": launches_per_step * K,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    if not args.skip_points:
+        T = 2048
+        toks = [int(t) for t in rng.integers(0, V, size=T)]
+        s = eng.open()
+        eng.step([(s, toks)])                              # warm-up
+        eng.close(s)
+        times = []
+        for _ in range(3):
+            s = eng.open()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([(s, toks)])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+            eng.close(s)
+        ms = min(times)
+        layer_params = sum(t.numel() for b in eng.model.blocks for t in
+                           (b.mixer.w_qkv, b.mixer.w_out, b.ffn.w_up, b.ffn.w_down))
+        flops = 2.0 * T * layer_params + 2.0 * T * T * cfg["hidden_size"] * layers + 2.0 * V * cfg["hidden_size"]
+        out["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                          "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+        b1, _, _ = decode_rate(1, min(K, 64), W, C)
+        b64, _, _ = decode_rate(64, min(K, 32), W, C)
+        out["points"] = {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

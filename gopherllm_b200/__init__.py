@@ -6,11 +6,11 @@ from parts, a paged cache with slots, one batched step function, a generation
 loop with sampling, and trace replay, on hand-written sm_100a kernels in
 bfloat16 and in true 32-bit.
 """
-from .api import LoadInfo, Model, load, write_random_model
+from .api import LoadInfo, Model, load, load_random, write_random_model
 from .engine.generate import (GenerationCanceled, GenerationOptions, GenerationResult,
                               GenerationStats)
 from .sampling.sampler import PRESETS, SamplerConfig
 
 __version__ = "0.1.0"
-__all__ = ["load", "write_random_model", "Model", "LoadInfo", "GenerationOptions",
+__all__ = ["load", "load_random", "write_random_model", "Model", "LoadInfo", "GenerationOptions",
            "GenerationResult", "GenerationStats", "GenerationCanceled", "SamplerConfig", "PRESETS"]

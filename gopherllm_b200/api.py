@@ -135,6 +135,44 @@ def load(path: str, dtype="bfloat16", max_tokens: Optional[int] = None, device="
     return Model(arch, config, engine, info)
 
 
+def load_random(config, seed: int = 0, dtype="bfloat16", max_tokens: Optional[int] = None,
+                device="cuda:0", max_slots: Optional[int] = None, layers: Optional[int] = None) -> Model:
+    """A model with seeded random weights built in memory: the tensors that
+    write_random_model(..., device=device) would write, without the folder.  ``layers``
+    keeps only the first so many layers (for machines or tests short of memory)."""
+    from .config.registry import architecture_from_config
+    from .weights.loader import random_tensors, resident_dtype
+    device = _require_cuda(device)
+    cdt = compute_dtype(dtype)
+    t0 = time.time()
+    raw = dict(config if isinstance(config, dict) else config.to_dict())
+    if layers is not None:
+        raw["num_hidden_layers"] = int(layers)
+    arch = architecture_from_config(raw)
+    cfg = arch.config_class.from_dict(raw)
+    model = build_model(arch, cfg)
+    table = tensor_table(model.parameters(), arch.tensor_names(cfg))
+    storage = STORAGE_DTYPES.get(str(getattr(cfg, "torch_dtype", "bfloat16")), torch.bfloat16)
+    sigma = float(getattr(cfg, "initializer_range", 0.02))
+    tensors = {}
+    with torch.cuda.device(device):
+        for name, t in random_tensors(table, seed, sigma, storage, device, to_cpu=False):
+            key, spec = table[name]
+            tensors[key] = t.to(resident_dtype(spec, storage, cdt)).contiguous()
+        model.load(tensors)
+        del tensors
+        if max_tokens is None:
+            max_tokens = 8 * model.spec.max_positions
+        cache = SequenceCache(model.cache_requests(), max_tokens, model.spec.max_positions,
+                              cdt, device, max_slots=max_slots)
+        engine = Engine(model, cache, cdt, device)
+    info = LoadInfo(path=f"random:{seed}", architecture=arch.name,
+                    dtype="bfloat16" if cdt == torch.bfloat16 else "float32",
+                    load_seconds=time.time() - t0, file_bytes=0, weight_bytes=model.weight_bytes(),
+                    cache_bytes=cache.bytes(), max_tokens=max_tokens)
+    return Model(arch, cfg, engine, info)
+
+
 def write_random_model(folder: str, config, seed: int = 0, device="cpu") -> None:
     """Write config.json and model.safetensors of a model with seeded random
     weights.  ``config`` is a config.json dict or a typed configuration.  Matrices

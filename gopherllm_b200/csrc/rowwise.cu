@@ -93,3 +93,31 @@ GL_API int gl_norm(const float* x, const int* rows, const float* gamma, const fl
         return GL_ERR_DTYPE;
     return gl_check_launch();
 }
+
+// ---------------------------------------------------------------------------
+// Feeding a decode step's choices back on the device: the sampled token becomes
+// the next input, positions and cached lengths move on by one, and the choice is
+// appended to a history so that several steps can run without the host.
+// ---------------------------------------------------------------------------
+__global__ void advance_kernel(int* tokens, int* tok_pos, int* seq_ctx, const int* sampled,
+                               int* history, int* counter, int B, int max_steps) {
+    const int b = threadIdx.x;
+    const int i = counter[0];
+    if (b < B) {
+        const int t = sampled[b];
+        if (i < max_steps) history[(size_t)i * B + b] = t;
+        tokens[b] = t;
+        tok_pos[b] += 1;
+        seq_ctx[b] += 1;
+    }
+    __syncthreads();
+    if (b == 0) counter[0] = i + 1;
+}
+
+GL_API int gl_advance_decode(int* tokens, int* tok_pos, int* seq_ctx, const int* sampled,
+                             int* history, int* counter, int B, int max_steps, cudaStream_t stream) {
+    if (B <= 0) return GL_OK;
+    if (B > 1024) return GL_ERR_SHAPE;
+    advance_kernel<<<1, ((B + 31) / 32) * 32, 0, stream>>>(tokens, tok_pos, seq_ctx, sampled, history, counter, B, max_steps);
+    return gl_check_launch();
+}

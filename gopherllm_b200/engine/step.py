@@ -75,6 +75,13 @@ class Engine:
         self.model, self.cache = model, cache
         self.act_dtype, self.device = act_dtype, torch.device(device)
         self.vocab = model.spec.vocab
+        # decode steps (one token per sequence) of the bfloat16 path replay a CUDA graph per
+        # batch shape; the 32-bit path always launches kernel by kernel
+        self.use_graphs = act_dtype == torch.bfloat16
+        self.graph_max_batch = 256
+        self._graphs: Dict[tuple, object] = {}
+        self._graph_pool = None
+        self.launches_per_loop_step: Dict[int, int] = {}    # kernels in one captured decode_loop step, by batch
         self._pinned: List[Optional[torch.Tensor]] = [None, None]
         self._events: List[Optional[torch.cuda.Event]] = [None, None]
         self._flip = 0
@@ -140,7 +147,8 @@ class Engine:
                     max_qlen=max(qlens), is_decode=max(qlens) == 1)
         return lay, buf, meta
 
-    def _upload(self, buf: np.ndarray) -> torch.Tensor:
+    def _stage(self, buf: np.ndarray) -> torch.Tensor:
+        """The descriptor in pinned host memory, ready for an asynchronous copy."""
         i = self._flip
         self._flip ^= 1
         if self._events[i] is not None:
@@ -150,13 +158,14 @@ class Engine:
             pin = torch.empty(max(buf.size, 4096), dtype=torch.int32, pin_memory=True)
             self._pinned[i] = pin
         pin[:buf.size].numpy()[...] = buf
-        dev = torch.empty(buf.size, dtype=torch.int32, device=self.device)
-        dev.copy_(pin[:buf.size], non_blocking=True)
+        self._staged = i
+        self.h2d_bytes_last = buf.size * 4
+        return pin[:buf.size]
+
+    def _staged_done(self) -> None:
         ev = torch.cuda.Event()
         ev.record()
-        self._events[i] = ev
-        self.h2d_bytes_last = buf.size * 4
-        return dev
+        self._events[self._staged] = ev
 
     def context(self, lay: _Layout, dev: torch.Tensor, meta: dict) -> StepContext:
         ctx = StepContext(self.device, self.act_dtype)
@@ -179,9 +188,112 @@ class Engine:
         (default: the last token of every run).  Returns float32 [wanted, vocab] on
         the device, in the order of runs and of want."""
         lay, buf, meta = self.plan(runs, want)
-        dev = self._upload(buf)
-        ctx = self.context(lay, dev, meta)
-        logits = self.model.forward(ctx, self.cache)
+        pin = self._stage(buf)
+        graph = None
+        if self.use_graphs and meta["is_decode"] and lay.B <= self.graph_max_batch:
+            graph = self._decode_graph(lay, meta)
+        if graph is not None:
+            graph.desc.copy_(pin, non_blocking=True)
+            self._staged_done()
+            graph.graph.replay()
+            logits = graph.logits
+        else:
+            dev = torch.empty(buf.size, dtype=torch.int32, device=self.device)
+            dev.copy_(pin, non_blocking=True)
+            self._staged_done()
+            logits = self.model.forward(self.context(lay, dev, meta), self.cache)
         for s, n in zip(meta["slots"], meta["new_lens"]):
             self.cache.commit(s, n)
         return logits
+
+    # -- CUDA graphs for decode steps -------------------------------------------
+    def _decode_graph(self, lay: _Layout, meta: dict):
+        """The captured step for this batch shape, or None the first time the shape is
+        seen (that step runs kernel by kernel, which also loads and warms every kernel).
+        The logits of a replayed step live in the graph's own buffer until the next
+        replay of the same shape."""
+        key = lay.key()
+        g = self._graphs.get(key)
+        if g is None:
+            self._graphs[key] = False
+            return None
+        if g is False:
+            g = _CapturedStep()
+            g.desc = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
+            bound = dict(meta)
+            bound["new_lens"] = [self.cache.max_positions]      # launch sizes must hold for any length
+            ctx = self.context(lay, g.desc, bound)
+            torch.cuda.synchronize(self.device)
+            g.graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(g.graph, pool=self._graph_pool):
+                g.logits = self.model.forward(ctx, self.cache)
+            self._graphs[key] = g
+        return g
+
+    @torch.no_grad()
+    def decode_loop(self, slots: Sequence[int], tokens: Sequence[int], steps: int, sampler) -> torch.Tensor:
+        """Run ``steps`` decode steps for these sequences wholly on the device: each step
+        feeds the tokens the sampler chose in the step before (the first step feeds
+        ``tokens``).  Pages for all steps are reserved first.  Returns the chosen tokens,
+        int32 [steps, len(slots)], on the device; nothing is copied to the host in between."""
+        from .. import ops
+        if steps < 1:
+            raise ValueError("steps must be at least 1")
+        cache = self.cache
+        B = len(slots)
+        ctxs = [cache.length(s) for s in slots]
+        cache.reserve([(s, c + steps) for s, c in zip(slots, ctxs)])
+        lay, buf, meta = self.plan([(s, [t]) for s, t in zip(slots, tokens)], None)
+        pin = self._stage(buf)
+        key = ("loop",) + lay.key()
+        g = self._graphs.get(key)
+        if g is None:
+            g = _CapturedStep()
+            g.desc = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
+            g.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+            g.history_cap = 4096
+            g.history = torch.zeros((g.history_cap, B), dtype=torch.int32, device=self.device)
+            g.state_row = torch.arange(B, dtype=torch.int32, device=self.device)
+            bound = dict(meta)
+            bound["new_lens"] = [cache.max_positions]
+            ctx = self.context(lay, g.desc, bound)
+
+            def body():
+                logits = self.model.forward(ctx, cache)
+                chosen = g.sampler.sample(logits, g.state_row)
+                ops.advance_decode(ctx.tokens, ctx.tok_pos, ctx.seq_ctx, chosen, g.history, g.counter)
+
+            g.sampler = sampler
+            g.desc.copy_(pin, non_blocking=True)
+            saved = [t.clone() for t in (sampler.rng, sampler.recent, sampler.recent_n)]
+            body()                                   # kernel by kernel once: loads and warms everything
+            for t, keep in zip((sampler.rng, sampler.recent, sampler.recent_n), saved):
+                t.copy_(keep)                        # the warm-up step drew nothing as far as the caller sees
+            torch.cuda.synchronize(self.device)
+            g.graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            before = ops.LAUNCHES
+            with torch.cuda.graph(g.graph, pool=self._graph_pool):
+                body()
+            self.launches_per_loop_step[B] = ops.LAUNCHES - before
+            self._graphs[key] = g
+        if g.sampler is not sampler:
+            raise ValueError("decode_loop was captured with another sampler for this batch size")
+        if steps > g.history_cap:
+            raise ValueError(f"decode_loop runs at most {g.history_cap} steps a call")
+        g.desc.copy_(pin, non_blocking=True)
+        self._staged_done()
+        g.counter.zero_()
+        for _ in range(steps):
+            g.graph.replay()
+        for s, c in zip(slots, ctxs):
+            cache.commit(s, c + steps)
+        return g.history[:steps]
+
+
+class _CapturedStep:
+    """A CUDA graph of one step with the buffers it reads and writes."""
+    desc = graph = logits = None

@@ -35,7 +35,12 @@ class KernelError(RuntimeError):
     pass
 
 
-def _check(code: int, what: str) -> None:
+LAUNCHES = 0       # kernels launched through this module since it was last set to 0
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += kernels
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
 
@@ -114,6 +119,22 @@ def norm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps
     _check(fn(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), c_int(dtype_code(out_dtype)),
               c_int(R), c_int(D), c_float(eps), c_int(1 if rms else 0), _stream()), "norm")
     return out
+
+
+def advance_decode(tokens, tok_pos, seq_ctx, sampled, history, counter) -> None:
+    """After a decode step on the device: tokens <- sampled, positions and cached lengths + 1,
+    history[counter] <- sampled, counter + 1 (all int32; history is [max_steps, B])."""
+    B = tokens.numel()
+    for n, t in (("tokens", tokens), ("tok_pos", tok_pos), ("seq_ctx", seq_ctx)):
+        _need(t, n, torch.int32, (B,))
+    _need(sampled, "sampled", torch.int32)
+    _need(history, "history", torch.int32)
+    _need(counter, "counter", torch.int32, (1,))
+    if sampled.numel() < B or history.shape[-1] != B:
+        raise KernelError("advance_decode: sampled or history does not match the batch")
+    fn = _lib("rowwise.cu").gl_advance_decode
+    _check(fn(_ptr(tokens), _ptr(tok_pos), _ptr(seq_ctx), _ptr(sampled), _ptr(history), _ptr(counter),
+              c_int(B), c_int(history.shape[0]), _stream()), "advance_decode")
 
 
 def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor):
@@ -292,7 +313,7 @@ def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, n
     a = _DecodeArgs(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                     seq_ctx.data_ptr(), pages.data_ptr(), part_o, part_ml,
                     B, num_heads, num_kv_heads, pages.shape[-1], window, splits)
-    _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode")
+    _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode", 2 if splits > 1 else 1)
 
 
 def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads: int,

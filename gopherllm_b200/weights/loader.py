@@ -120,7 +120,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 
 def random_tensors(table: Dict[str, Tuple[str, ParamSpec]], seed: int, sigma: float,
-                   storage: torch.dtype, device="cpu") -> Iterator[Tuple[str, torch.Tensor]]:
+                   storage: torch.dtype, device="cpu", to_cpu: bool = True
+                   ) -> Iterator[Tuple[str, torch.Tensor]]:
     """(name, tensor) for every declared tensor, each from a generator seeded by
     (seed, name) so values do not depend on the order of generation.  Matrices
     N(0, sigma); biases and norm offsets N(0, 0.02); norm scales 1 + N(0, 0.02).
@@ -142,7 +143,8 @@ def random_tensors(table: Dict[str, Tuple[str, ParamSpec]], seed: int, sigma: fl
             t = torch.zeros_like(z)
         else:
             raise ValueError(f"{name}: unknown initialisation {spec.init!r}")
-        yield name, t.to(storage).cpu()
+        t = t.to(storage)
+        yield name, (t.cpu() if to_cpu else t)
 
 
 def write_model_folder(folder: str, config_dict: dict, table: Dict[str, Tuple[str, ParamSpec]],

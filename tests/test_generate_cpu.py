@@ -1,0 +1,75 @@
+"""The generation loop's decisions and the options' rules (no device needed)."""
+import pytest
+
+from gopherllm_b200.engine.generate import GenerationOptions, SequenceState, pages_for, plan_batches
+from gopherllm_b200.sampling.sampler import PRESETS, SamplerConfig, recent_window, request_seed
+from gopherllm_b200.cli import build_parser, effective_sampler, parse_duration, parse_prompts
+
+
+def test_accept_order_stop_emit_length_feed():
+    # runtime.go:1130-1165: a stop token is neither emitted nor fed
+    s = SequenceState([1, 2, 3], max_tokens=3, stop_tokens=[9], max_positions=100)
+    assert s.accept(5) and s.generated == [5] and s.fed == 4
+    assert not s.accept(9) and s.finish_reason == "stop" and s.generated == [5] and s.fed == 4
+    with pytest.raises(RuntimeError):
+        s.accept(1)
+    s = SequenceState([1, 2, 3], max_tokens=2, stop_tokens=[], max_positions=100)
+    assert s.accept(5)
+    assert not s.accept(6) and s.finish_reason == "length" and s.generated == [5, 6] and s.fed == 4
+    # the cache cannot take another position: the token is emitted, not fed
+    s = SequenceState([1, 2, 3], max_tokens=50, stop_tokens=[], max_positions=4)
+    assert s.accept(5) and s.fed == 4
+    assert not s.accept(6) and s.finish_reason == "length" and s.generated == [5, 6]
+
+
+def test_plan_batches():
+    P = 64
+    # worst-case pages: prompt + every token it may feed, capped by the longest sequence
+    assert pages_for(10, 20, 2048) == 1 and pages_for(60, 5, 2048) == 2 and pages_for(2000, 500, 2048) == 32
+    assert plan_batches([10, 10, 10], 20, 2048, page_budget=2, slot_budget=8) == [[0, 1], [2]]
+    assert plan_batches([10] * 5, 20, 2048, page_budget=100, slot_budget=2) == [[0, 1], [2, 3], [4]]
+    assert plan_batches([100, 10, 300], 28, 2048, page_budget=6, slot_budget=8) == [[0, 1], [2]]
+    with pytest.raises(ValueError, match="empty"):
+        plan_batches([3, 0], 5, 64, 10, 10)
+    with pytest.raises(ValueError, match="does not fit"):
+        plan_batches([64], 5, 64, 10, 10)                 # len(tokens) >= MaxSeqLen (runtime.go:866-868)
+    with pytest.raises(ValueError, match="the cache holds"):
+        plan_batches([500], 500, 2048, page_budget=4, slot_budget=1)
+
+
+def test_option_rules():
+    GenerationOptions().validate()
+    with pytest.raises(ValueError, match="max_tokens"):
+        GenerationOptions(max_tokens=0).validate()
+    bad = [dict(temperature=-1), dict(temperature=float("nan")), dict(top_p=0), dict(top_p=1.5),
+           dict(top_k=-1), dict(min_p=2), dict(repeat_penalty=0)]
+    for kw in bad:
+        with pytest.raises(ValueError):
+            GenerationOptions(sampler=SamplerConfig(**kw)).validate()
+    d = SamplerConfig()
+    assert (d.temperature, d.top_p, d.top_k, d.min_p, d.repeat_penalty) == (0.7, 0.9, 40, 0.0, 1.1)
+    assert PRESETS["deterministic"].is_greedy and PRESETS["creative"].top_k == 80
+    o = GenerationOptions.from_kwargs(None, max_tokens=5, temperature=0.0, stop_tokens=[1, 2], seed=7)
+    assert o.max_tokens == 5 and o.sampler.is_greedy and o.stop_tokens == (1, 2) and o.seed == 7
+    with pytest.raises(TypeError):
+        GenerationOptions.from_kwargs(None, max_new_tokens=5)
+
+
+def test_seeds_and_window():
+    assert request_seed(5, 0) == 5 and request_seed(5, 3) == 8
+    assert request_seed(0, 0) == 0xDEADBEEFCAFE1337          # zero is remapped (sampling.go:30-35)
+    assert request_seed(2 ** 64 - 1, 1) == 0xDEADBEEFCAFE1337
+    assert recent_window(list(range(100))) == list(range(36, 100)) and recent_window([1, 2]) == [1, 2]
+
+
+def test_cli_options():
+    assert parse_prompts("1, 2 3;4") == [[1, 2, 3], [4]]
+    assert parse_duration("2m") == 120 and parse_duration("1h30m") == 5400 and parse_duration("500ms") == 0.5
+    assert parse_duration("7") == 7.0
+    with pytest.raises(SystemExit):
+        parse_duration("soon")
+    a = build_parser().parse_args(["m", "--preset", "precise", "--temp", "0.5", "-n", "7", "--top-k", "3"])
+    s = effective_sampler(a)
+    assert (s.temperature, s.top_k, s.top_p, s.repeat_penalty) == (0.5, 3, 0.9, 1.05) and a.max_tokens == 7
+    a = build_parser().parse_args(["m"])
+    assert effective_sampler(a) == SamplerConfig() and a.max_tokens == 256 and a.bench_runs == 3

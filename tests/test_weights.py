@@ -1,0 +1,170 @@
+"""Weights: container, checks with one clear error, resident types, random mode (no device needed)."""
+import json
+import os
+import shutil
+import tempfile
+
+import pytest
+import torch
+
+import plain_phi
+import tiny
+from gopherllm_b200.api import build_model, write_random_model
+from gopherllm_b200.config import load_config
+from gopherllm_b200.parts.base import ParamSpec
+from gopherllm_b200.weights.loader import (WeightsError, check_folder, load_folder, resident_dtype,
+                                           tensor_table)
+from gopherllm_b200.weights.safetensors_io import TensorFile, index_folder, read_header, write_file
+
+
+def table_for(folder):
+    arch, cfg = load_config(folder)
+    model = build_model(arch, cfg)
+    return model, tensor_table(model.parameters(), arch.tensor_names(cfg))
+
+
+def rewrite(folder, edit):
+    """Copy a model folder, letting ``edit`` change the {name: tensor} dict."""
+    d = tempfile.mkdtemp(prefix="gl_w_")
+    shutil.copy(os.path.join(folder, "config.json"), d)
+    entries = index_folder(folder)
+    with TensorFile(entries) as tf:
+        tensors = {n: tf.get(n).clone() for n in entries}
+    edit(tensors)
+    write_file(os.path.join(d, "model.safetensors"), tensors.items())
+    return d
+
+
+def test_container_round_trip_and_independent_reader():
+    d = tempfile.mkdtemp()
+    ts = {"a": torch.arange(6, dtype=torch.float32).reshape(2, 3), "b.c": torch.randn(5).to(torch.bfloat16),
+          "i": torch.tensor([1, -2, 3], dtype=torch.int32), "e": torch.zeros(0, 4), "s": torch.tensor(2.5)}
+    path = os.path.join(d, "model.safetensors")
+    write_file(path, ts.items(), metadata={"k": 1})
+    entries, meta = read_header(path)
+    assert meta == {"k": "1"} and set(entries) == set(ts)
+    with TensorFile(entries) as tf:
+        for n, t in ts.items():
+            got = tf.get(n)
+            assert got.dtype == t.dtype and tuple(got.shape) == tuple(t.shape) and torch.equal(got, t)
+    # the package the rest of the world uses reads the same bytes
+    from safetensors import safe_open
+    with safe_open(path, "pt") as f:
+        for n, t in ts.items():
+            assert torch.equal(f.get_tensor(n), t)
+
+
+def test_container_rejects_damage():
+    d = tempfile.mkdtemp()
+    path = os.path.join(d, "model.safetensors")
+    write_file(path, [("a", torch.zeros(4, 4))])
+    raw = open(path, "rb").read()
+    open(path, "wb").write(raw[:-8])
+    with pytest.raises(ValueError, match="exceeds file length"):
+        read_header(path)
+    open(path, "wb").write(b"\xff" * 4)
+    with pytest.raises(ValueError):
+        read_header(path)
+    with pytest.raises(FileNotFoundError):
+        index_folder(tempfile.mkdtemp())
+
+
+def test_names_follow_the_architecture():
+    model, table = table_for(tiny.folder("B"))
+    names = set(table)
+    assert "model.embed_tokens.weight" in names and "model.final_layernorm.bias" in names
+    assert "lm_head.bias" in names and "lm_head.weight" not in names          # tied
+    for i in range(3):
+        for t in ("input_layernorm.weight", "self_attn.q_proj.weight", "self_attn.k_proj.bias",
+                  "self_attn.v_proj.weight", "self_attn.dense.bias", "self_attn.q_layernorm.weight",
+                  "self_attn.k_layernorm.bias", "mlp.fc1.weight", "mlp.fc2.bias"):
+            assert f"model.layers.{i}.{t}" in names
+    _, table_a = table_for(tiny.folder("A"))
+    assert "lm_head.weight" in table_a and not any("layernorm.weight" in n and "self_attn" in n for n in table_a)
+    check_folder(tiny.folder("A"), table_a)
+    # the plain implementation's own reader sees the same tensors
+    cfg, W = plain_phi.read_folder(tiny.folder("A"))
+    assert set(W) == set(table_a)
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes():
+    src = tiny.folder("A")
+    _, table = table_for(src)
+
+    def edit(t):
+        del t["model.layers.1.mlp.fc2.bias"]
+        del t["lm_head.weight"]
+        t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(4)
+        t["model.layers.0.mlp.fc1.weight"] = torch.zeros(255, 64, dtype=torch.bfloat16)
+        t["model.final_layernorm.weight"] = torch.zeros(64, dtype=torch.int32)
+    bad = rewrite(src, edit)
+    with pytest.raises(WeightsError) as e:
+        check_folder(bad, table)
+    msg = str(e.value)
+    assert e.value.missing == ["lm_head.weight", "model.layers.1.mlp.fc2.bias"]
+    assert e.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert len(e.value.wrong) == 2
+    for needle in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes or types (2)",
+                   "model.layers.0.mlp.fc1.weight is [255, 64], the model wants [256, 64]", "stored as I32"):
+        assert needle in msg, needle
+
+
+def test_tied_head_may_lack_its_bias_and_carry_a_copy():
+    src = tiny.folder("B")
+    _, table = table_for(src)
+
+    def edit(t):
+        del t["lm_head.bias"]
+        t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    d = rewrite(src, edit)
+    with pytest.raises(WeightsError):
+        check_folder(d, table)                                  # the copy is unexpected unless told
+    check_folder(d, table, ignore=("lm_head.weight",))
+    tensors, _ = load_folder(d, table, torch.float32, "cpu", ignore=("lm_head.weight",))
+    assert torch.count_nonzero(tensors["head/bias"]) == 0
+
+
+def test_resident_types():
+    m, v, i = ParamSpec((2, 2)), ParamSpec((2,), "vector"), ParamSpec((2,), "table_int")
+    bf, f32, f16 = torch.bfloat16, torch.float32, torch.float16
+    assert resident_dtype(m, bf, bf) == bf            # kept in bfloat16
+    assert resident_dtype(m, f32, bf) == f32          # stored in 32-bit stays so
+    assert resident_dtype(m, f16, bf) == f32
+    assert resident_dtype(m, bf, f32) == f32          # the 32-bit path widens everything
+    assert resident_dtype(v, bf, bf) == f32
+    assert resident_dtype(i, torch.int64, bf) == torch.int32
+    src = tiny.folder("A")
+
+    def edit(t):
+        t["model.layers.0.mlp.fc1.weight"] = t["model.layers.0.mlp.fc1.weight"].float()
+    d = rewrite(src, edit)
+    _, table = table_for(d)
+    got, nbytes = load_folder(d, table, bf, "cpu")
+    assert got["layers/0/ffn/up.weight"].dtype == f32 and got["layers/1/ffn/up.weight"].dtype == bf
+    assert got["layers/0/norm/weight"].dtype == f32 and got["embedding"].dtype == bf and nbytes > 0
+
+
+def test_random_mode_is_seeded_and_shaped():
+    cfg = dict(tiny.TINY_A)
+    a, b, c = tempfile.mkdtemp(), tempfile.mkdtemp(), tempfile.mkdtemp()
+    write_random_model(a, cfg, seed=3)
+    write_random_model(b, cfg, seed=3)
+    write_random_model(c, cfg, seed=4)
+    assert json.load(open(os.path.join(a, "config.json")))["hidden_size"] == 64
+    _, Wa = plain_phi.read_folder(a)
+    _, Wb = plain_phi.read_folder(b)
+    _, Wc = plain_phi.read_folder(c)
+    assert all(torch.equal(Wa[n], Wb[n]) for n in Wa)
+    assert not torch.equal(Wa["lm_head.weight"], Wc["lm_head.weight"])
+    w = Wa["model.layers.0.mlp.fc1.weight"]
+    assert abs(w.std().item() - 0.02) < 0.002 and abs(w.mean().item()) < 0.002
+    g = Wa["model.layers.1.input_layernorm.weight"]
+    assert abs(g.mean().item() - 1.0) < 0.02 and 0.005 < g.std().item() < 0.04
+    assert 0.005 < Wa["model.layers.1.self_attn.dense.bias"].std().item() < 0.04
+    cfg_b = dict(tiny.TINY_B)
+    d = tempfile.mkdtemp()
+    write_random_model(d, cfg_b, seed=1)
+    _, Wd = plain_phi.read_folder(d)
+    assert abs(Wd["model.layers.0.mlp.fc1.weight"].std().item() - 0.05) < 0.004      # initializer_range
+    model, table = table_for(d)
+    check_folder(d, table)
