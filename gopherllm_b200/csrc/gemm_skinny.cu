@@ -1,26 +1,26 @@
 // out[M,N] = act(A[M,K] · W[N,K]ᵀ + bias) + add0 + add1 for few rows (M <= 64), bfloat16.
 //
 // With few tokens a product is a stream of weights: every weight is read once
-// and the machine is bound by HBM.  The kernel therefore turns the product
-// round: the weight rows are the 16-row operand of mma.sync.m16n8k16 and the
-// tokens the 8-column operand, and each thread fetches its fragments straight
-// from global memory with 16-byte loads (8 consecutive k for one row).  Because
-// both operands are indexed by the same k, taking the same 8 consecutive k for
-// slots {2t,2t+1,2t+8,2t+9} of two successive MMAs in both operands is only a
-// renaming of k and leaves the sum unchanged.
+// and the machine is bound by HBM, so what counts is bytes in flight.  A block
+// owns 64 weight rows and a range of K.  Weights and activations arrive in
+// shared memory by TMA (cp.async.bulk.tensor, 64 k per stage, 128-byte swizzle so
+// that ldmatrix reads without bank conflicts; one thread issues, an mbarrier per
+// stage counts the bytes), several stages ahead, and the product is turned round
+// for mma.sync.m16n8k16: the weight rows are the 16-row operand, the tokens the
+// 8-column operand.  Rows and columns outside the matrices read as zero.
 //
-// A block is 4 warps x 16 weight rows.  To fill 148 SMs when N is small, K is cut
-// over the blocks of a thread-block cluster; the partial tiles meet in
-// distributed shared memory, each block reducing and finishing (bias,
-// activation, residual adds) its share of the tile's columns in a fixed order,
-// so the result does not depend on timing.
+// To fill 148 SMs when N is small, K is cut over the blocks of a thread-block
+// cluster; the partial tiles meet in distributed shared memory, each block
+// reducing and finishing (bias, activation, residual adds) its share of the
+// tile's columns in rank order, so the result does not depend on timing.
 #include "common.cuh"
+#include "tma.cuh"
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
 
 #define SK_ROWS 64          // weight rows per block
+#define SK_BK 64            // k per pipeline stage (128 bytes per row)
 #define SK_THREADS 128
-#define SK_UNROLL 4         // k-steps of 32 whose weight loads are issued together
 
 struct GemmArgs {
     const void* a;        // [M, K] bf16
@@ -32,13 +32,13 @@ struct GemmArgs {
     int M, N, K, act;
 };
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+__device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-
+__device__ __forceinline__ void ldmatrix_x2(unsigned addr, unsigned& r0, unsigned& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -46,27 +46,39 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, typename TO>
+// byte offset of 16-byte chunk c of row r in a tile of 128-byte rows
+__device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
+
+template <int MT, int STAGES, typename TO>
 __global__ void __launch_bounds__(SK_THREADS)
-gemm_skinny_kernel(GemmArgs g, int k_per_block) {
-    extern __shared__ float tile[];                       // [MT*8][SK_ROWS + 1]
+gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensorMap map_w,
+                   const __grid_constant__ CUtensorMap map_a) {
+    extern __shared__ unsigned char smem_raw[];
+    constexpr int W_BYTES = SK_ROWS * 128, A_BYTES = MT * 8 * 128, STAGE = W_BYTES + A_BYTES;
     constexpr int LD = SK_ROWS + 1;
     cg::cluster_group cluster = cg::this_cluster();
-    const int S = (int)cluster.num_blocks();
-    const int rank = (int)cluster.block_rank();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int grp = lane >> 2, t = lane & 3;
+    const int S = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.y * SK_ROWS;
     const int kb = blockIdx.x * k_per_block;
     const int ke = min(g.K, kb + k_per_block);
-    const __nv_bfloat16* W = (const __nv_bfloat16*)g.w;
-    const __nv_bfloat16* A = (const __nv_bfloat16*)g.a;
-    const int r0 = min(n0 + warp * 16 + grp, g.N - 1), r1 = min(n0 + warp * 16 + grp + 8, g.N - 1);
-    const __nv_bfloat16* w0 = W + (size_t)r0 * g.K;
-    const __nv_bfloat16* w1 = W + (size_t)r1 * g.K;
-    const __nv_bfloat16* arow[MT];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) arow[mt] = A + (size_t)min(mt * 8 + grp, g.M - 1) * g.K;
+    const int iters = ke > kb ? (ke - kb + SK_BK - 1) / SK_BK : 0;
+    // stages start on a 1024-byte boundary (the swizzle pattern repeats every 8 rows of 128 bytes)
+    unsigned char* smem = smem_raw + ((1024u - (gl_smem_u32(smem_raw) & 1023u)) & 1023u);
+    const unsigned base = gl_smem_u32(smem);
+    const unsigned bars = base + STAGES * STAGE;            // one 8-byte mbarrier per stage
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    auto load_stage = [&](int it) {                           // one thread
+        const unsigned sb = base + (it % STAGES) * STAGE, bar = bars + 8 * (it % STAGES);
+        mbar_expect_tx(bar, STAGE);
+        tma_load_2d(sb, &map_w, kb + it * SK_BK, n0, bar);
+        tma_load_2d(sb + W_BYTES, &map_a, kb + it * SK_BK, 0, bar);
+    };
 
     float acc[MT][4];
 #pragma unroll
@@ -74,42 +86,50 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[mt][e] = 0.f;
 
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int k0 = kb; k0 < ke; k0 += 32 * SK_UNROLL) {
-        uint4 wa[SK_UNROLL], wb[SK_UNROLL];
+    if (tid == 0)
+        for (int s = 0; s < STAGES - 1 && s < iters; ++s) load_stage(s);
+    for (int it = 0; it < iters; ++it) {
+        if (!mbar_wait(bars + 8 * (it % STAGES), (it / STAGES) & 1)) break;
+        __syncthreads();                                      // everyone is done with the stage refilled next
+        if (tid == 0 && it + STAGES - 1 < iters) load_stage(it + STAGES - 1);
+        const unsigned sb = base + (it % STAGES) * STAGE;
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
-            const int kk = k0 + 32 * u + 8 * t;
-            const bool ok = kk < ke;
-            wa[u] = ok ? ldg_stream(w0 + kk) : zero;
-            wb[u] = ok ? ldg_stream(w1 + kk) : zero;
-        }
-#pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
-            const int kk = k0 + 32 * u + 8 * t;
-            const bool ok = kk < ke;
+        for (int kk = 0; kk < SK_BK / 16; ++kk) {
+            unsigned a0, a1, a2, a3;
+            {
+                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int c = kk * 2 + (lane >> 4);
+                ldmatrix_x4(sb + swz(r, c), a0, a1, a2, a3);
+            }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                const uint4 x = ok ? *(const uint4*)(arow[mt] + kk) : zero;
-                mma_bf16(acc[mt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, x.x, x.y);
-                mma_bf16(acc[mt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, x.z, x.w);
+                unsigned b0, b1;
+                const int r = mt * 8 + (lane & 7);
+                const int c = kk * 2 + ((lane >> 3) & 1);
+                ldmatrix_x2(sb + W_BYTES + swz(r, c), b0, b1);
+                mma_bf16(acc[mt], a0, a1, a2, a3, b0, b1);
             }
         }
     }
-    // partial tile to shared memory: tile[m][n_local]
+    __syncthreads();
+    // partial tile to shared memory (the pipeline's buffers are free now): tile[m][n_local]
+    float* tile = (float*)smem;
+    {
+        const int grp = lane >> 2, t = lane & 3;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        const int m = mt * 8 + 2 * t, nl = warp * 16 + grp;
-        tile[m * LD + nl] = acc[mt][0];
-        tile[(m + 1) * LD + nl] = acc[mt][1];
-        tile[m * LD + nl + 8] = acc[mt][2];
-        tile[(m + 1) * LD + nl + 8] = acc[mt][3];
+        for (int mt = 0; mt < MT; ++mt) {
+            const int m = mt * 8 + 2 * t, nl = warp * 16 + grp;
+            tile[m * LD + nl] = acc[mt][0];
+            tile[(m + 1) * LD + nl] = acc[mt][1];
+            tile[m * LD + nl + 8] = acc[mt][2];
+            tile[(m + 1) * LD + nl + 8] = acc[mt][3];
+        }
     }
     cluster.sync();
     // this block finishes columns [rank*cnt, (rank+1)*cnt) of the tile, summing the blocks in rank order
     const int cnt = SK_ROWS / S;
     TO* O = (TO*)g.out;
-    for (int i = threadIdx.x; i < MT * 8 * cnt; i += SK_THREADS) {
+    for (int i = tid; i < MT * 8 * cnt; i += SK_THREADS) {
         const int m = i / cnt, nl = rank * cnt + (i - m * cnt);
         const int n = n0 + nl;
         if (m >= g.M || n >= g.N) continue;
@@ -128,13 +148,35 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block) {
     cluster.sync();       // nobody leaves while a peer may still read its tile
 }
 
-template <int MT, typename TO>
+template <int MT, int STAGES>
+static constexpr size_t skinny_smem() {
+    // stages + barriers + room to align the start; the reduction tile reuses the stages
+    return (size_t)STAGES * (SK_ROWS * 128 + MT * 8 * 128) + 8 * STAGES + 1024;
+}
+static_assert(4 * (SK_ROWS * 128 + 8 * 8 * 128) >= 8 * 8 * (SK_ROWS + 1) * 4, "reduction tile fits the stages");
+
+template <int MT, int STAGES, typename TO>
 static int launch_skinny(const GemmArgs& g, int S, cudaStream_t stream) {
-    const int k_per_block = ((g.K + S - 1) / S + 31) / 32 * 32;
+    constexpr size_t smem = skinny_smem<MT, STAGES>();
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_skinny_kernel<MT, STAGES, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return GL_ERR_SMEM;
+        }
+        configured = true;
+    }
+    const int k_per_block = ((g.K + S - 1) / S + SK_BK - 1) / SK_BK * SK_BK;
+    CUtensorMap map_w, map_a;
+    int rc = gl_cached_map_bf16(&map_w, g.w, (uint64_t)g.N, (uint64_t)g.K, SK_ROWS, SK_BK);
+    if (rc != GL_OK) return rc;
+    rc = gl_cached_map_bf16(&map_a, g.a, (uint64_t)g.M, (uint64_t)g.K, MT * 8, SK_BK);
+    if (rc != GL_OK) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S, (g.N + SK_ROWS - 1) / SK_ROWS, 1);
     cfg.blockDim = dim3(SK_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = (size_t)MT * 8 * (SK_ROWS + 1) * sizeof(float);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -144,19 +186,34 @@ static int launch_skinny(const GemmArgs& g, int S, cudaStream_t stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (cfg.gridDim.y > 65535) return GL_ERR_SHAPE;
-    if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<MT, TO>, g, k_per_block) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<MT, STAGES, TO>, g, k_per_block, map_w, map_a) != cudaSuccess) {
         cudaGetLastError();
         return GL_ERR_LAUNCH;
     }
     return GL_OK;
 }
 
+// blocks of one SM that fit by shared memory, for each M bucket
+static int blocks_per_sm(int M) {
+    const size_t smem = M <= 8 ? skinny_smem<1, 6>() : M <= 16 ? skinny_smem<2, 6>()
+                      : M <= 32 ? skinny_smem<4, 5>() : skinny_smem<8, 4>();
+    const int n = (int)((227 * 1024) / (smem + 1024));
+    return n < 1 ? 1 : (n > 8 ? 8 : n);
+}
+
 template <typename TO>
 static int dispatch_m(const GemmArgs& g, int S, cudaStream_t stream) {
-    if (g.M <= 8) return launch_skinny<1, TO>(g, S, stream);
-    if (g.M <= 16) return launch_skinny<2, TO>(g, S, stream);
-    if (g.M <= 32) return launch_skinny<4, TO>(g, S, stream);
-    return launch_skinny<8, TO>(g, S, stream);
+    if (g.M <= 8) return launch_skinny<1, 6, TO>(g, S, stream);
+    if (g.M <= 16) return launch_skinny<2, 6, TO>(g, S, stream);
+    if (g.M <= 32) return launch_skinny<4, 5, TO>(g, S, stream);
+    return launch_skinny<8, 4, TO>(g, S, stream);
+}
+
+// 1 if a bounded wait of this library ever ran out (the result of that launch is invalid)
+GL_API int gl_gemm_skinny_wait_failed() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, gl_wait_failed, sizeof(int)) != cudaSuccess) return -1;
+    return v;
 }
 
 // split_k: 0 lets the launcher choose; else 1, 2, 4 or 8 blocks of a cluster share K
@@ -167,9 +224,18 @@ GL_API int gl_gemm_skinny(const GemmArgs* args, int out_dtype, int split_k, cuda
     if (((uintptr_t)g.a | (uintptr_t)g.w) & 15) return GL_ERR_ALIGN;
     int S = split_k;
     if (S == 0) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        // as many blocks as are resident at once, while every block keeps a few stages of K
         const int tiles = (g.N + SK_ROWS - 1) / SK_ROWS;
+        const int slots = sms * blocks_per_sm(g.M);
         S = 1;
-        while (S < 8 && tiles * S * 4 < 2400 && g.K / (S * 2) >= 256) S *= 2;
+        while (S < 8 && tiles * S * 2 <= slots && g.K / (S * 2) >= 4 * SK_BK) S *= 2;
     }
     if (S != 1 && S != 2 && S != 4 && S != 8) return GL_ERR_SHAPE;
     if (out_dtype == GL_F32) return dispatch_m<float>(g, S, stream);

@@ -271,12 +271,22 @@ def sm_count(device) -> int:
     return _SM_COUNT[idx]
 
 
-def decode_splits(batch: int, num_kv_heads: int, max_len: int, device) -> int:
-    """How many blocks share one (sequence, key/value head): enough to put about four
-    blocks on every SM, never more than the longest sequence has pages."""
+def decode_blocks_per_sm(head_dim: int, group: int = 1) -> int:
+    """Blocks of the decode kernel one SM holds at once (bounded by shared memory)."""
+    gm = 1 if group <= 1 else 2 if group == 2 else 4 if group <= 4 else 8
+    kg = 128 // (head_dim // 8)
+    smem = 4 * PAGE * (2 * head_dim + 16) + 4 * (gm * head_dim + gm * PAGE + gm * 8 + kg * head_dim)
+    return max(1, min(8, (227 * 1024) // (smem + 1024)))
+
+
+def decode_splits(batch: int, num_kv_heads: int, max_len: int, device, head_dim: int = 80,
+                  group: int = 1) -> int:
+    """How many blocks share one (sequence, key/value head): as many as keep the whole
+    grid resident at once (a grid a little larger than the machine would run a second,
+    nearly empty wave), never more than the longest sequence has pages."""
     pages = max(1, -(-max_len // PAGE))
-    want = -(-4 * sm_count(device) // max(1, batch * num_kv_heads))
-    return max(1, min(want, pages, 64))
+    slots = sm_count(device) * decode_blocks_per_sm(head_dim, group)
+    return max(1, min(slots // max(1, batch * num_kv_heads), pages, 64))
 
 
 def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, num_kv_heads: int,
@@ -323,7 +333,8 @@ def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads
     cached lengths on the device; the longest query run and sequence on the host)."""
     if (ctx.is_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
             and head_dim % 16 == 0 and num_heads // num_kv_heads <= DECODE_MAX_GROUP):
-        splits = decode_splits(ctx.n_seqs, num_kv_heads, ctx.max_len, q.device)
+        splits = decode_splits(ctx.n_seqs, num_kv_heads, ctx.max_len, q.device, head_dim,
+                               num_heads // num_kv_heads)
         attention_decode(q, out, k_cache, v_cache, ctx.seq_ctx, pages, num_heads, num_kv_heads,
                          head_dim, splits, window)
         return
