@@ -4,7 +4,7 @@ from __future__ import annotations
 from typing import Iterable, Iterator, Tuple
 
 # libraries that do not depend on a model's sizes
-GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu", "gemm_skinny.cu",
+GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_tcgen05.cu",
            "sampling.cu")
 
 # libraries compiled once per head size (GL_HEAD_DIM)

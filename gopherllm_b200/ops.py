@@ -381,6 +381,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
 
 
 SKINNY_MAX_ROWS = 64
+USE_TCGEN05 = True
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
@@ -400,6 +401,34 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
+                 add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+                 tile_n: int = 0) -> torch.Tensor:
+    """The tensor-core product (tcgen05.mma fed by TMA, accumulators in tensor memory) for
+    bfloat16 operands with K a multiple of 8; meant for many rows."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    if out is None:
+        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    g = _gemm_args(a, w, bias, act, add0, add1, out)
+    if a.shape[1] % 8:
+        raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
+    if tile_n not in (0, 64, 128, 256):
+        raise KernelError("tile_n is 0 (choose), 64, 128 or 256")
+    fn = _lib("gemm_tcgen05.cu").gl_gemm_tcgen05
+    _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(tile_n), _stream()), "gemm_tcgen05")
+    return out
+
+
+def wait_failures() -> dict:
+    """Which libraries recorded a bounded wait that ran out (their last results are invalid)."""
+    out = {}
+    for src, fn in (("gemm_tcgen05.cu", "gl_gemm_tcgen05_wait_failed"), ("gemm_skinny.cu", "gl_gemm_skinny_wait_failed")):
+        out[src] = int(getattr(_lib(src), fn)())
+    return out
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
            add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -408,6 +437,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0:
         if a.shape[0] <= SKINNY_MAX_ROWS:
             return gemm_skinny(a, w, bias, act, add0, add1, out_dtype, out)
+        if USE_TCGEN05:
+            return gemm_tcgen05(a, w, bias, act, add0, add1, out_dtype, out)
     return gemm_simt(a, w, bias, act, add0, add1, out_dtype, out)
 
 

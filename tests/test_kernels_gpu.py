@@ -79,6 +79,51 @@ def test_gemm_skinny(M, N, K):
         o.gemm_skinny(rnd(65, K, dtype=torch.bfloat16), w)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (65, 40, 160), (200, 1000, 200),
+                                   (300, 777 * 8, 416), (2048, 2560, 2560), (1000, 7680, 2568)])
+def test_gemm_tcgen05(M, N, K):
+    o = ops()
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    bias, add0, add1 = rnd(N, seed=2), rnd(M, N, seed=3), rnd(M, N, seed=4)
+    ref = ref_linear(a, w, bias, "gelu_new", add0, add1)
+    for tile in (0, 64, 128, 256):
+        got = o.gemm_tcgen05(a, w, bias, "gelu_new", add0, add1, out_dtype=torch.float32, tile_n=tile)
+        torch.cuda.synchronize()
+        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        err = (got.double() - ref).abs().max().item()
+        assert err <= 3e-5 * max(1.0, ref.abs().max().item()), (tile, err)
+    got = o.gemm_tcgen05(a, w, bias, None, out_dtype=torch.bfloat16)
+    ref = ref_linear(a, w, bias, None, None, None)
+    assert (got.double() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item())
+    x = add0.clone()                                                   # in place on the residual stream
+    o.gemm_tcgen05(a, w, bias, None, x, add1, out=x)
+    assert (x.double() - ref_linear(a, w, bias, None, add0, add1)).abs().max() <= 3e-5 * max(1.0, ref.abs().max().item())
+
+
+def test_gemm_tcgen05_one_weight_stands_out():
+    """A single large weight must reach exactly one output column, wherever it sits in K and N."""
+    o = ops()
+    M, N, K = 130, 520, 1096
+    a = torch.ones(M, K, dtype=torch.bfloat16, device=DEV)
+    for (n, k) in [(0, 0), (519, 1095), (77, 1029), (256, 63), (255, 64), (128, 15), (127, 16), (511, 1088)]:
+        w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
+        w[n, k] = 3.0
+        for tile in (64, 128, 256):
+            got = o.gemm_tcgen05(a, w, out_dtype=torch.float32, tile_n=tile)
+            want = torch.zeros(M, N, device=DEV)
+            want[:, n] = 3.0
+            assert torch.equal(got, want), (n, k, tile)
+    # and a single activation reaches exactly one row
+    w = torch.ones(N, K, dtype=torch.bfloat16, device=DEV)
+    for (m, k) in [(0, 0), (129, 1095), (64, 520), (127, 7), (128, 8)]:
+        a = torch.zeros(M, K, dtype=torch.bfloat16, device=DEV)
+        a[m, k] = 2.0
+        got = o.gemm_tcgen05(a, w, out_dtype=torch.float32)
+        want = torch.zeros(M, N, device=DEV)
+        want[m, :] = 2.0
+        assert torch.equal(got, want), (m, k)
+
+
 def test_gemm_skinny_one_weight_stands_out():
     """A single large weight far along K must reach exactly one output."""
     o = ops()
