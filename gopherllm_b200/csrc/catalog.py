@@ -8,7 +8,7 @@ GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu",
            "sampling.cu")
 
 # libraries compiled once per head size (GL_HEAD_DIM)
-PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu",)
+PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu")
 
 
 def head_dim_defines(head_dim: int) -> Tuple[str, ...]:

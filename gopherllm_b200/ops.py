@@ -253,6 +253,21 @@ def attention_generic(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, p
            "attention_generic")
 
 
+def attention_prefill(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+                      num_heads: int, num_kv_heads: int, head_dim: int, max_qlen: int,
+                      window: int = 0) -> None:
+    """Causal attention of runs of new tokens over the bfloat16 cache on tensor cores
+    (mma.sync, 32-bit softmax); head sizes 16..256 in steps of 16."""
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise KernelError(f"prefill attention takes head sizes 16..256 in steps of 16, not {head_dim}")
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise KernelError("prefill attention takes bfloat16 queries and cache")
+    a = _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+                   num_heads, num_kv_heads, head_dim, window, max_qlen, 1.0)
+    lib = _lib("attention_prefill.cu", catalog.head_dim_defines(head_dim))
+    _check(lib.gl_attention_prefill(byref(a), _stream()), "attention_prefill")
+
+
 class _DecodeArgs(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("seq_ctx", c_void_p), ("pages", c_void_p), ("part_o", c_void_p), ("part_ml", c_void_p),
@@ -337,6 +352,10 @@ def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads
                                num_heads // num_kv_heads)
         attention_decode(q, out, k_cache, v_cache, ctx.seq_ctx, pages, num_heads, num_kv_heads,
                          head_dim, splits, window)
+        return
+    if q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0:
+        attention_prefill(q, out, k_cache, v_cache, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_ctx, pages,
+                          num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)
         return
     attention_generic(q, out, k_cache, v_cache, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_ctx, pages,
                       num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)

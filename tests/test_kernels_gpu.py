@@ -199,12 +199,21 @@ def ref_attention(q, k, v, ctx, qlen, window):
     return out
 
 
+@pytest.mark.parametrize("nH,nKV,hd", [(3, 3, 16), (4, 2, 80), (6, 1, 48), (2, 2, 256), (5, 5, 32), (2, 2, 128)])
+@pytest.mark.parametrize("window", [0, 37, 150])
+def test_attention_prefill(nH, nKV, hd, window):
+    run_attention("prefill", torch.bfloat16, nH, nKV, hd, window, [0, 130, 63, 5, 200], [70, 1, 66, 9, 300])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nH,nKV,hd", [(3, 3, 16), (4, 2, 80), (6, 1, 48), (2, 2, 256), (5, 5, 40)])
 @pytest.mark.parametrize("window", [0, 37])
 def test_attention_generic(dtype, nH, nKV, hd, window):
+    run_attention("generic", dtype, nH, nKV, hd, window, [0, 130, 63, 5], [70, 1, 66, 9])
+
+
+def run_attention(kernel, dtype, nH, nKV, hd, window, ctxs, qlens):
     o = ops()
-    ctxs, qlens = [0, 130, 63, 5], [70, 1, 66, 9]
     B, L = len(ctxs), max(c + q for c, q in zip(ctxs, qlens))
     k = rnd(B, L, nKV, hd, seed=1).to(dtype).float()
     v = rnd(B, L, nKV, hd, seed=2).to(dtype).float()
@@ -215,8 +224,9 @@ def test_attention_generic(dtype, nH, nKV, hd, window):
     out = torch.empty(T, nH * hd, dtype=dtype, device=DEV)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     starts = np.concatenate([[0], np.cumsum(qlens)[:-1]]).tolist()
-    o.attention_generic(q.reshape(T, nH * hd), out, kc, vc, i32(starts), i32(qlens), i32(ctxs), table,
-                        nH, nKV, hd, max(qlens), window)
+    fn = o.attention_generic if kernel == "generic" else o.attention_prefill
+    fn(q.reshape(T, nH * hd), out, kc, vc, i32(starts), i32(qlens), i32(ctxs), table,
+       nH, nKV, hd, max(qlens), window)
     tol = 2e-5 if dtype == torch.float32 else 2 ** -7
     for b in range(B):
         ref = ref_attention(q[starts[b]:starts[b] + qlens[b]].double().cpu(), k[b, :lens[b]].double().cpu(),
@@ -250,7 +260,7 @@ def test_attention_decode(nH, nKV, hd, window):
             assert (got - ref).abs().max() <= 2 ** -7 * max(1.0, ref.abs().max().item()), (b, splits)
 
 
-@pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode"])
+@pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode", "prefill"])
 def test_attention_far_key_and_window_edge(kernel):
     """One key among hundreds carries the whole weight: its value must come back.  With a
     window the key at the window's edge is seen and the one before it is not."""
@@ -271,6 +281,8 @@ def test_attention_far_key_and_window_edge(kernel):
         qd = q.reshape(1, nH * hd).to(dtype).to(DEV)
         if kernel == "decode":
             o.attention_decode(qd, out, kc, vc, i32([L - 1]), table, nH, nKV, hd, 3, window)
+        elif kernel == "prefill":
+            o.attention_prefill(qd, out, kc, vc, i32([0]), i32([1]), i32([L - 1]), table, nH, nKV, hd, 1, window)
         else:
             o.attention_generic(qd, out, kc, vc, i32([0]), i32([1]), i32([L - 1]), table, nH, nKV, hd, 1, window)
         got = out.reshape(nH, hd).float().cpu()
