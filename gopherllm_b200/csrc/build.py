@@ -83,7 +83,7 @@ def library_path(source: str, defines: Tuple[str, ...] = (), build: bool = True,
     for d in _build_dirs():
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
+            probe = os.path.join(d, f".w{os.getpid()}_{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)
@@ -91,7 +91,7 @@ def library_path(source: str, defines: Tuple[str, ...] = (), build: bool = True,
             last_err = e
             continue
         so, stamp = os.path.join(d, name + ".so"), os.path.join(d, name + ".hash")
-        tmp = os.path.join(d, f"{name}.{os.getpid()}.tmp.so")
+        tmp = os.path.join(d, f"{name}.{os.getpid()}_{threading.get_ident()}.tmp.so")
         cmd = [_nvcc(), *_ARCH_FLAGS, *_BASE_FLAGS, *[f"-D{x}" for x in defines],
                "-I", _HERE, "-o", tmp, os.path.join(_HERE, source)]
         if verbose:
