@@ -275,3 +275,47 @@ GL_API int gl_attention_decode(const DecodeArgs* args, cudaStream_t stream) {
     }
     return gl_check_launch();
 }
+
+// ---------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate device memory.
+// See attention_decode_static.h for who that is and what the limits are.
+// ---------------------------------------------------------------------------
+#include "attention_decode_static.h"
+
+// Scratch for the splits' partial results, resident in every GPU context that
+// loads this library until the process exits.
+static __device__ __align__(256) float gl_decode_static_scratch[GL_DECODE_STATIC_SCRATCH_FLOATS];
+
+#define GL_DECODE_STATIC_MAX_DEVICES 64
+static float* gl_decode_static_ptr[GL_DECODE_STATIC_MAX_DEVICES];   // device address of the array, per device
+
+GL_API long long gl_attention_decode_static_capacity() { return GL_DECODE_STATIC_SCRATCH_FLOATS; }
+
+GL_API int gl_attention_decode_static(const DecodeArgs* args, cudaStream_t stream) {
+    if (!args) return GL_ERR_SHAPE;
+    DecodeArgs a = *args;
+    if (a.B <= 0) return GL_OK;
+    if (a.splits < 1 || a.nH <= 0) return GL_ERR_SHAPE;
+    const long long need = gl_attention_decode_scratch(a.B, a.nH, a.splits);
+    if (need > (long long)GL_DECODE_STATIC_SCRATCH_FLOATS) return GL_ERR_SCRATCH;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= GL_DECODE_STATIC_MAX_DEVICES) {
+        cudaGetLastError();
+        return GL_ERR_DRIVER;
+    }
+    if (!gl_decode_static_ptr[dev]) {
+        // In host code the array's name is only a handle; the address a kernel can use is
+        // looked up once per device, with that device current.
+        float* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, gl_decode_static_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return GL_ERR_DRIVER;
+        }
+        gl_decode_static_ptr[dev] = p;
+    }
+    // Every (sequence, head, split) cell that the merge reads is written by the first kernel of
+    // the same call, empty splits included, so nothing has to be cleared between calls.
+    a.part_o = gl_decode_static_ptr[dev];
+    a.part_ml = gl_decode_static_ptr[dev] + (size_t)a.B * a.nH * a.splits * AD_HD;
+    return gl_attention_decode(&a, stream);
+}

@@ -26,6 +26,7 @@ enum GlError {
     GL_ERR_LAUNCH = -4,     // cudaGetLastError() after the launch was not success
     GL_ERR_SMEM = -5,       // shared memory need exceeds the device limit
     GL_ERR_DRIVER = -6,     // a driver entry point could not be obtained or failed
+    GL_ERR_SCRATCH = -7,    // the call needs more scratch than a built-in array holds
 };
 
 // tokens of the cache that share one page

@@ -28,6 +28,7 @@ _ERRORS = {
     -4: "the launch failed (cudaGetLastError)",
     -5: "the kernel needs more shared memory than the device allows",
     -6: "a CUDA driver entry point is missing or failed",
+    -7: "the call needs more scratch than the library's built-in array holds",
 }
 
 
