@@ -50,6 +50,11 @@ class DecoderModel:
         self.head_weight = self.embedding if self.spec.tie_embeddings else tensors["head/weight"]
         self.head_bias = tensors.get("head/bias")
 
+    @property
+    def capturable(self) -> bool:
+        """True if a step of this model can be recorded into a CUDA graph."""
+        return self.final_norm.capturable and all(b.capturable for b in self.blocks)
+
     def weight_bytes(self) -> int:
         seen, n = set(), 0
         for t in self._all_tensors():

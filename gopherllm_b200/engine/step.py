@@ -77,7 +77,7 @@ class Engine:
         self.vocab = model.spec.vocab
         # decode steps (one token per sequence) of the bfloat16 path replay a CUDA graph per
         # batch shape; the 32-bit path always launches kernel by kernel
-        self.use_graphs = act_dtype == torch.bfloat16
+        self.use_graphs = act_dtype == torch.bfloat16 and bool(getattr(model, "capturable", False))
         self.graph_max_batch = 256
         self._graphs: Dict[tuple, object] = {}
         self._graph_pool = None

@@ -16,6 +16,7 @@ class Attention(Mixer):
     q and k, position encoding, query scale, cache write, attention over the
     cache, output projection.  Grouped-query attention when num_kv_heads <
     num_heads (query head h reads group h / (nH/nKV), model.go:2828)."""
+    capturable = True
 
     def __init__(self, spec: MixerSpec):
         if spec.num_heads % spec.num_kv_heads:

@@ -50,7 +50,13 @@ class StateRequest:
 
 
 class Part:
-    """Common protocol of every part."""
+    """Common protocol of every part.
+
+    capturable: True if ``forward`` only launches work on the current stream (no copy to
+    the host, no host-side decision on device data), so a step can be recorded into a
+    CUDA graph.  The default is False: a part must opt in.
+    """
+    capturable = False
 
     def parameters(self) -> Dict[str, ParamSpec]:
         return {}

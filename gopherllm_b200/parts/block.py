@@ -36,6 +36,10 @@ class _AssembledBlock(Block):
     def cache_request(self):
         return self.mixer.cache_request()
 
+    @property
+    def capturable(self):
+        return all(part.capturable for _, part in self._children())
+
 
 class ParallelBlock(_AssembledBlock):
     """x ← x + ffn(n) + mixer(n), n = norm(x): one norm feeds both branches

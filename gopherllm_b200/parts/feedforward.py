@@ -14,6 +14,7 @@ class DenseFeedForward(FeedForward):
     """down(act(up(x))) with biases: the plain, ungated MLP (model.go:2758-2772,
     forward_batch.go:537-581).  The activation runs in the first product's
     epilogue, the additions to the residual in the second's."""
+    capturable = True
 
     def __init__(self, spec: FeedForwardSpec):
         if spec.activation not in ops.ACTIVATIONS:

@@ -13,6 +13,7 @@ from .base import Norm, ParamSpec, register_norm
 class LayerNorm(Norm):
     """y = (x - mean) * rsqrt(var + eps) * weight + bias, biased variance, in
     32-bit with the reciprocal square root in 64-bit (bert.go:748-776)."""
+    capturable = True
     rms = False
 
     def __init__(self, spec: NormSpec):

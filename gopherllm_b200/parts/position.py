@@ -25,6 +25,7 @@ class Rope(PositionEncoding):
     angle float32(pos) * inv[i] is a 32-bit product; sine and cosine are taken
     in 64-bit (prepareRopeScratch, model.go:3041-3046).  The tables depend on
     the step's positions only, so every layer of a step shares them."""
+    capturable = True
 
     def __init__(self, spec: PositionSpec):
         if spec.rotary_dim % 2:
@@ -45,6 +46,7 @@ class Rope(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    capturable = True
     def __init__(self, spec: PositionSpec):
         self.spec = spec
 

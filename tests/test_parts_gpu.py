@@ -1,0 +1,327 @@
+"""Each part alone against the plain implementation, and parts defined outside the package."""
+import math
+import os
+import tempfile
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_phi
+import tiny
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def harness(requests, dtype, hidden, vocab=50, max_tokens=1024, max_positions=300):
+    """A cache and an engine-like context builder for parts run on their own."""
+    from gopherllm_b200.cache.sequence_cache import SequenceCache
+    from gopherllm_b200.engine.step import Engine
+
+    class Stub:
+        class spec:
+            pass
+    Stub.spec.vocab = vocab
+    cache = SequenceCache(requests, max_tokens, max_positions, dtype, DEV)
+    eng = Engine(Stub(), cache, dtype, DEV)
+    eng.use_graphs = False
+    return cache, eng
+
+
+def context(eng, runs):
+    lay, buf, meta = eng.plan(runs, None)
+    dev = torch.from_numpy(buf).to(DEV)
+    ctx = eng.context(lay, dev, meta)
+    for s, n in zip(meta["slots"], meta["new_lens"]):
+        eng.cache.commit(s, n)
+    return ctx
+
+
+def rand(shape, seed, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from gopherllm_b200.config import NormSpec
+    from gopherllm_b200.parts import build_norm
+    x = rand((9, 160), 1, 2.0).to(DEV)
+    for kind, bias in (("layernorm", True), ("rmsnorm", False)):
+        n = build_norm(NormSpec(kind, 160, 1e-6, bias=bias))
+        params = {k: (1.0 + rand(v.shape, 2, 0.1) if k == "weight" else rand(v.shape, 3, 0.1)).to(DEV)
+                  for k, v in n.parameters().items()}
+        assert set(params) == ({"weight", "bias"} if bias else {"weight"})
+        n.load(params)
+        got = n.forward(x, dtype).double().cpu()
+        xd = x.double().cpu()
+        if kind == "layernorm":
+            ref = plain_phi.layer_norm(xd, params["weight"].double().cpu(), params["bias"].double().cpu(), 1e-6)
+        else:
+            ref = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-6) * params["weight"].double().cpu()
+        tol = 1e-5 if dtype == torch.float32 else 2 ** -8
+        assert (got - ref).abs().max() <= tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_attention_part_whole_and_in_pieces(dtype, qk_norm):
+    """The mixer alone: whole sequence in one step equals prefix + single tokens, and both equal
+    the plain formulas (projection, head norm, rotation, scale, causal softmax, projection)."""
+    from gopherllm_b200.config import MixerSpec, NormSpec, PositionSpec
+    from gopherllm_b200.parts import build_mixer
+    D, nH, nKV, hd, rot, T = 96, 6, 2, 32, 16, 70
+    spec = MixerSpec("attention", D, nH, nKV, hd, 0, 1 / math.sqrt(hd), True,
+                     NormSpec("layernorm", hd, 1e-5, True) if qk_norm else None,
+                     PositionSpec("rope", rot, 10000.0))
+    mixer = build_mixer(spec)
+    P = {k: (rand(v.shape, 10 + i, 0.08) + (1.0 if k.endswith("norm.weight") else 0.0))
+         for i, (k, v) in enumerate(sorted(mixer.parameters().items()))}
+    store = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    P = {k: v.to(store).float() for k, v in P.items()}
+    mixer.load({k: (v.to(dtype) if v.dim() == 2 else v).to(DEV) for k, v in P.items()})
+    xn = rand((T, D), 5).to(dtype)
+    # plain
+    xd = xn.double()
+    W = {k: v.double() for k, v in P.items()}
+    q = (xd @ W["q.weight"].T + W["q.bias"]).reshape(T, nH, hd)
+    k = (xd @ W["k.weight"].T + W["k.bias"]).reshape(T, nKV, hd)
+    v = (xd @ W["v.weight"].T + W["v.bias"]).reshape(T, nKV, hd)
+    if qk_norm:
+        q = plain_phi.layer_norm(q, W["q_norm.weight"], W["q_norm.bias"], 1e-5)
+        k = plain_phi.layer_norm(k, W["k_norm.weight"], W["k_norm.bias"], 1e-5)
+    sin, cos = plain_phi.rope_tables(range(T), rot, 10000.0)
+    q, k = plain_phi.apply_rope(q, sin, cos, rot) / math.sqrt(hd), plain_phi.apply_rope(k, sin, cos, rot)
+    ref = plain_phi.attention(q, k, v).reshape(T, nH * hd) @ W["out.weight"].T + W["out.bias"]
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    for cut in (T, 40):
+        cache, eng = harness([mixer.cache_request()], dtype, D)
+        s = cache.open()
+        outs = []
+        pieces = [list(range(cut))] + [[t] for t in range(cut, T)]
+        for piece in pieces:
+            ctx = context(eng, [(s, [0] * len(piece))])
+            add = torch.ones(len(piece), D, device=DEV)
+            out = torch.empty(len(piece), D, device=DEV)
+            mixer.forward(xn[piece].to(DEV), ctx, cache.view(0), (add,), out)
+            outs.append(out.double().cpu() - 1.0)
+        got = torch.cat(outs)
+        assert (got - ref).abs().max() <= tol * max(1.0, ref.abs().max().item()), cut
+        cache.close(s)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act", ["gelu_new", "gelu", "relu"])
+def test_feed_forward_part(dtype, act):
+    from gopherllm_b200.config import FeedForwardSpec
+    from gopherllm_b200.parts import build_feed_forward
+    D, I, T = 72, 200, 11
+    ffn = build_feed_forward(FeedForwardSpec("dense", D, I, act, True))
+    store = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    P = {k: rand(v.shape, 20 + i, 0.1).to(store).float() for i, (k, v) in enumerate(sorted(ffn.parameters().items()))}
+    ffn.load({k: (v.to(dtype) if v.dim() == 2 else v).to(DEV) for k, v in P.items()})
+    xn = rand((T, D), 6).to(dtype)
+    W = {k: v.double() for k, v in P.items()}
+    ref = plain_phi.mlp(xn.double(), W["up.weight"], W["up.bias"], W["down.weight"], W["down.bias"], act)
+    _, eng = harness([], dtype, D)
+
+    class Ctx:
+        act_dtype = dtype
+    a0, a1 = rand((T, D), 7).to(DEV), rand((T, D), 8).to(DEV)
+    out = torch.empty(T, D, device=DEV)
+    ffn.forward(xn.to(DEV), Ctx, (a0, a1), out)
+    got = out.double().cpu() - a0.double().cpu() - a1.double().cpu()
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert (got - ref).abs().max() <= tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_blocks(dtype):
+    """The parallel block equals the plain phi block; the sequential arrangement equals its formula."""
+    from gopherllm_b200.config import PhiConfig, resolve_architecture
+    from gopherllm_b200.config.specs import BlockSpec
+    from gopherllm_b200.parts import build_block
+    cfg = dict(tiny.TINY_C)
+    spec = resolve_architecture("phi").build_spec(PhiConfig.from_dict(cfg))
+    bs = spec.layers[0]
+    T, D = 50, cfg["hidden_size"]
+    pcfg, Wf = plain_phi.read_folder(tiny.folder("C"))
+    names = resolve_architecture("phi").tensor_names(PhiConfig.from_dict(cfg))
+    x0 = rand((T, D), 9)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    for arrangement in ("parallel", "sequential"):
+        b = build_block(BlockSpec(arrangement, bs.norm, bs.mixer, bs.ffn, bs.norm if arrangement == "sequential" else None))
+        tensors = {}
+        for key, ps in b.parameters().items():
+            slot, pk = key.split("/")
+            src = names.layer(0, "norm" if slot == "norm2" else slot, pk)
+            t = Wf[src].float()
+            tensors[key] = (t.to(dtype) if ps.kind == "matrix" else t).to(DEV)
+        b.load(tensors)
+        cache, eng = harness([b.cache_request()], dtype, D)
+        s = cache.open()
+        x = x0.clone().to(DEV)
+        b.forward(x, context(eng, [(s, [0] * T)]), cache.view(0))
+        if arrangement == "parallel":
+            ref = plain_phi.phi_block(x0.double(), list(range(T)), Wf, 0, pcfg)
+        else:
+            # x + attn(norm(x)), then + mlp(norm(that)): build it from the plain parts
+            zero = {k: torch.zeros_like(v) for k, v in Wf.items() if ".mlp." in k}
+            only_attn = plain_phi.phi_block(x0.double(), list(range(T)), {**Wf, **zero}, 0, pcfg)
+            pre = "model.layers.0."
+            n2 = plain_phi.layer_norm(only_attn, Wf[pre + "input_layernorm.weight"], Wf[pre + "input_layernorm.bias"],
+                                      pcfg["layer_norm_eps"])
+            ref = only_attn + plain_phi.mlp(n2, Wf[pre + "mlp.fc1.weight"], Wf[pre + "mlp.fc1.bias"],
+                                            Wf[pre + "mlp.fc2.weight"], Wf[pre + "mlp.fc2.bias"], pcfg["hidden_act"])
+        assert (x.double().cpu() - ref).abs().max() <= tol * max(1.0, ref.abs().max().item()), arrangement
+
+
+# ---------------------------------------------------------------------------
+# parts and an architecture defined here, outside the package
+# ---------------------------------------------------------------------------
+def define_toy():
+    """A mixer with state of its own (an exponential moving sum over a sequence's tokens, one
+    state row per sequence), a toy architecture that alternates it with attention, and their
+    registration.  Nothing inside gopherllm_b200 is edited."""
+    from gopherllm_b200.config import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
+                                       ScheduleEntry)
+    from gopherllm_b200.config.registry import Architecture, register_architecture, resolve_architecture
+    from gopherllm_b200.parts import Mixer, ParamSpec, StateRequest, register_mixer
+
+    class EmaMixer(Mixer):
+        def __init__(self, spec):
+            self.spec, self.decay = spec, float(spec.option("decay", 0.5))
+
+        def parameters(self):
+            return {"proj.weight": ParamSpec((self.spec.hidden, self.spec.hidden))}
+
+        def load(self, t):
+            self.w = t["proj.weight"]
+
+        def cache_request(self):
+            return StateRequest((self.spec.hidden,))
+
+        def forward(self, xn, ctx, cache, add, out):
+            starts, lens, slots = ctx.seq_qstart.tolist(), ctx.seq_qlen.tolist(), ctx.seq_slot.tolist()
+            y = torch.empty(xn.shape, dtype=torch.float32, device=xn.device)
+            for b in range(ctx.n_seqs):
+                s = cache.rows[slots[b]]
+                for t in range(starts[b], starts[b] + lens[b]):
+                    s.mul_(self.decay).add_(xn[t].float())
+                    y[t] = s
+            res = y @ self.w.float().T
+            for a in add:
+                res = res + a
+            out.copy_(res)
+            return out
+
+    if resolve_architecture("toy-ema") is None:
+        register_mixer("ema", EmaMixer)
+
+        @dataclass
+        class ToyConfig:
+            hidden_size: int = 48
+            vocab_size: int = 90
+            decay: float = 0.5
+            torch_dtype: str = "bfloat16"
+            initializer_range: float = 0.1
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+            def to_dict(self):
+                return dict(architectures=["ToyEmaForCausalLM"], model_type="toy-ema", **self.__dict__)
+
+        def spec_of(c):
+            norm = NormSpec("rmsnorm", c.hidden_size, 1e-5, bias=False)
+            ema = MixerSpec("ema", c.hidden_size, extra=(("decay", c.decay),))
+            att = MixerSpec("attention", c.hidden_size, 3, 1, 16, 0, 0.25, False, None, PositionSpec("rope", 16, 100.0))
+            ffn = FeedForwardSpec("dense", c.hidden_size, 64, "relu", False)
+            layers = (BlockSpec("sequential", norm, ema, ffn, norm), BlockSpec("parallel", norm, att, ffn),
+                      BlockSpec("sequential", norm, ema, ffn, norm))
+            # layer 0 runs twice, each run with state of its own
+            sched = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 2), ScheduleEntry(0, 3))
+            return ModelSpec(c.hidden_size, c.vocab_size, 128, layers, sched, norm, tie_embeddings=True, head_bias=False)
+
+        class Names:
+            embedding, final_norm, head = "emb.weight", "norm_f", "head"
+
+            def __init__(self, c):
+                pass
+
+            def layer(self, i, slot, key):
+                return f"h.{i}.{slot}.{key}"
+
+        register_architecture(Architecture("toy-ema", ToyConfig, spec_of, Names), aliases=["ToyEma"])
+    return resolve_architecture("toy-ema")
+
+
+def toy_plain(tokens, W, decay):
+    """The toy model written out plainly (float64): sequential EMA blocks, one parallel attention block."""
+    def rms(x, w):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * w
+
+    def ffn(x, i):
+        return torch.relu(x @ W[f"h.{i}.ffn.up.weight"].T) @ W[f"h.{i}.ffn.down.weight"].T
+
+    def ema_block(x, i):
+        n = rms(x, W[f"h.{i}.norm.weight"])
+        s, ys = torch.zeros(x.shape[1], dtype=x.dtype), []
+        for t in range(x.shape[0]):
+            s = decay * s + n[t]
+            ys.append(s)
+        x = x + torch.stack(ys) @ W[f"h.{i}.mixer.proj.weight"].T
+        return x + ffn(rms(x, W[f"h.{i}.norm2.weight"]), i)
+
+    def att_block(x, i):
+        T = x.shape[0]
+        n = rms(x, W[f"h.{i}.norm.weight"])
+        q = (n @ W[f"h.{i}.mixer.q.weight"].T).reshape(T, 3, 16)
+        k = (n @ W[f"h.{i}.mixer.k.weight"].T).reshape(T, 1, 16)
+        v = (n @ W[f"h.{i}.mixer.v.weight"].T).reshape(T, 1, 16)
+        sin, cos = plain_phi.rope_tables(range(T), 16, 100.0)
+        q, k = plain_phi.apply_rope(q, sin, cos, 16) * 0.25, plain_phi.apply_rope(k, sin, cos, 16)
+        a = plain_phi.attention(q, k, v).reshape(T, 48) @ W[f"h.{i}.mixer.out.weight"].T
+        return (x + ffn(n, i)) + a
+
+    x = W["emb.weight"][torch.tensor(tokens)]
+    for i in (0, 1, 2, 0):
+        x = att_block(x, i) if i == 1 else ema_block(x, i)
+    return rms(x, W["norm_f.weight"]) @ W["emb.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_registered_built_and_stepped(dtype):
+    import gopherllm_b200 as gl
+    arch = define_toy()
+    cfg = arch.config_class()
+    folder = tempfile.mkdtemp(prefix="gl_toy_")
+    gl.write_random_model(folder, cfg.to_dict(), seed=3)
+    m = gl.load(folder, dtype=dtype, max_tokens=512)
+    assert m.architecture.name == "toy-ema"
+    cache = m.engine.cache
+    assert len(cache.groups) == 1 and len(cache._states) == 3          # one attention entry, three state entries
+    _, W = plain_phi.read_folder(folder)
+    rng = np.random.default_rng(4)
+    seqs = [tiny.prompt(rng, n, cfg.vocab_size) for n in (30, 7, 64)]
+    refs = [toy_plain(s, W, cfg.decay).numpy() for s in seqs]
+    tol = dict(float32=2e-4, bfloat16=3e-2)[dtype]
+    for round_ in range(2):                                            # the second round reuses slots: state must restart at zero
+        slots = [m.open_sequence() for _ in seqs]
+        cut = [20, 3, 64]
+        out = m.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], [list(range(c)) for c in cut]).cpu().numpy()
+        o = 0
+        for i, c in enumerate(cut):
+            assert np.abs(out[o:o + c] - refs[i][:c]).max() <= tol * max(1.0, np.abs(refs[i]).max()), (round_, i)
+            o += c
+        for t in range(max(len(s) - c for s, c in zip(seqs, cut))):
+            live = [i for i in range(3) if cut[i] + t < len(seqs[i])]
+            out = m.step([(slots[i], [seqs[i][cut[i] + t]]) for i in live]).cpu().numpy()
+            for r, i in enumerate(live):
+                assert np.abs(out[r] - refs[i][cut[i] + t]).max() <= tol * max(1.0, np.abs(refs[i]).max()), (round_, i, t)
+        for sl in slots:
+            m.close_sequence(sl)
+    got = m.generate(seqs[1], max_tokens=5, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, stop_tokens=())
+    assert len(got.tokens) == 5
