@@ -79,3 +79,21 @@ def test_sampler_rules():
         assert plain_phi.sample(lg, 1.0, 4, 1.0, 0.5, 1.0, rng, []) in (1, 2)
     for _ in range(200):                                                                  # nucleus: 0.46 > 0.4
         assert plain_phi.sample(lg, 1.0, 4, 0.4, 0.0, 1.0, rng, []) == 1
+
+
+def test_golden_outputs_are_unchanged():
+    """tests/golden/plain_tiny.json pins the plain implementation and the seeded weights."""
+    import json
+    import os
+    import sys
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, here)
+    import make_golden
+    now = make_golden.compute()
+    with open(os.path.join(here, "plain_tiny.json")) as f:
+        then = json.load(f)
+    for name in then:
+        assert now[name]["tokens"] == then[name]["tokens"]
+        assert now[name]["argmax"] == then[name]["argmax"]
+        assert np.allclose(now[name]["last_row_first_8"], then[name]["last_row_first_8"], atol=2e-6)
+        assert np.allclose(now[name]["row_sums"], then[name]["row_sums"], atol=2e-4)
