@@ -2,14 +2,19 @@
 // values, bandwidth-bound, so the work is cut over (sequence, key/value head,
 // split of the sequence's pages) to fill the machine, and merged afterwards.
 //
-// A block streams its pages through shared memory with cp.async (16-byte
-// copies, two pages in flight), scores 64 keys at a time, keeps a running
-// maximum and sum in 32-bit and accumulates the weighted values in 32-bit
-// registers.  Splits write (max, sum, unnormalised output) to scratch and a
-// second kernel merges them; with one split the block writes the result itself.
-// The head size is a compile-time constant (GL_HEAD_DIM, a multiple of 16).
+// A block streams its pages through shared memory with cp.async (16-byte copies,
+// AD_STAGES pages in flight).  Inside a page each of the 4 warps owns 16 of the 64
+// keys and runs a softmax of its own over them: scores are one mma.sync.m16n8k16
+// chain (keys as the 16-row operand, the up to 8 query heads that share the
+// key/value head as the 8 columns), maximum, sum and rescaling are 32-bit, and the
+// weighted values are a second chain (values transposed by ldmatrix as the 16-row
+// operand) into 32-bit accumulators.  The warps never wait for one another inside
+// the loop except at the barrier that hands a page buffer back; their four partial
+// softmaxes are merged at the end.  Splits write (max, sum, unnormalised output)
+// to scratch and a second kernel merges them; with one split the block writes the
+// result itself.  The head size is a compile-time constant (GL_HEAD_DIM, a
+// multiple of 16).
 #include "common.cuh"
-#include <cuda_pipeline.h>
 
 #ifndef GL_HEAD_DIM
 #define GL_HEAD_DIM 80
@@ -18,11 +23,14 @@ static_assert(GL_HEAD_DIM % 16 == 0 && GL_HEAD_DIM >= 16 && GL_HEAD_DIM <= 256, 
 
 #define AD_THREADS 128
 #define AD_HD GL_HEAD_DIM
+#define AD_KS (AD_HD / 16)                          // 16-wide steps along the head size
 #define AD_CHUNKS (AD_HD / 8)                       // 16-byte chunks per row
-#define AD_ROW (AD_HD * 2 + 16)                     // padded row in bytes: conflict-free 16-byte reads
+#define AD_ROW (AD_HD * 2 + 16)                     // padded row in bytes: conflict-free ldmatrix
 #define AD_TILE (GL_PAGE * AD_ROW)                  // one page of K (or V) for one head
-#define AD_KG (AD_THREADS / AD_CHUNKS)              // key groups in the value pass
-#define AD_MAXG 8                                   // query heads per key/value head handled at once
+#ifndef AD_STAGES
+#define AD_STAGES 2                                 // pages of K and V in flight per block
+#endif
+#define AD_MAXG 8                                   // query heads per key/value head (the 8 columns of the MMA)
 
 struct DecodeArgs {
     const __nv_bfloat16* q;      // [B, nH*hd], scaled
@@ -36,30 +44,53 @@ struct DecodeArgs {
     int B, nH, nKV, max_pages, window, splits;
 };
 
-__device__ __forceinline__ void load_page(unsigned char* dst, const __nv_bfloat16* src) {
-    // 64 rows of hd bf16, contiguous in global memory, to padded rows in shared memory
-    for (int i = threadIdx.x; i < GL_PAGE * AD_CHUNKS; i += AD_THREADS) {
+__device__ __forceinline__ unsigned ad_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ad_cp16(unsigned dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void ad_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void ad_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ad_ldm4(unsigned addr, unsigned (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ad_ldm4t(unsigned addr, unsigned (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ad_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// rows [0, n_valid) of a page (64 rows of hd bf16, contiguous) to padded rows; the rest is zero,
+// so that what an earlier sequence left in the page cannot reach a product
+__device__ __forceinline__ void ad_load_page(unsigned dst, const __nv_bfloat16* src, int n_valid) {
+    // 64 * hd / 8 chunks over 128 threads: hd / 16 chunks a thread, at fixed (row, column) places
+#pragma unroll
+    for (int j = 0; j < AD_KS; ++j) {
+        const int i = threadIdx.x + j * AD_THREADS;
         const int r = i / AD_CHUNKS, c = i - r * AD_CHUNKS;
-        __pipeline_memcpy_async(dst + r * AD_ROW + c * 16, (const unsigned char*)src + (size_t)i * 16, 16);
+        const bool ok = r < n_valid;
+        ad_cp16(dst + r * AD_ROW + c * 16, ok ? (const void*)((const unsigned char*)src + (size_t)i * 16) : (const void*)src,
+                ok ? 16 : 0);
     }
 }
 
-// GM: compile-time bound on the query heads per key/value head (1, 2, 4 or 8), so that the
-// per-head accumulators stay in registers
-template <int GM>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    unsigned char* Kt[2] = {smem, smem + 2 * AD_TILE};
-    unsigned char* Vt[2] = {smem + AD_TILE, smem + 3 * AD_TILE};
-    float* qs = (float*)(smem + 4 * AD_TILE);            // [G][hd]
-    float* ps = qs + GM * AD_HD;                         // [G][64] scores, then weights
-    float* red = ps + GM * GL_PAGE;                      // [G][4] warp maxima, [G][4] warp sums
-    float* osum = red + GM * 8;                     // [KG][hd] final reduction, one head at a time
+    // stage s: keys at 2 s AD_TILE, values one tile further; then per-warp scratch
+    const unsigned sbase = ad_smem(smem);
+    __nv_bfloat16* pw = (__nv_bfloat16*)(smem + 2 * AD_STAGES * AD_TILE);      // [4 warps][8 heads][16 keys]
+    float* mrg = (float*)(smem + 2 * AD_STAGES * AD_TILE + 4 * 8 * 16 * 2);    // [4][8][2] then [4][hd][G]
 
     const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int G = a.nH / a.nKV;                          // query heads of this key/value head (<= AD_MAXG)
+    const int grp = lane >> 2, t = lane & 3;
+    const int G = a.nH / a.nKV;                          // query heads of this key/value head (<= 8)
     const int pos = a.seq_ctx[b];                        // the query's position; keys lo..pos
     const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
     const int first_page = lo / GL_PAGE, n_pages = pos / GL_PAGE + 1 - first_page;
@@ -70,141 +101,151 @@ attn_decode_kernel(DecodeArgs a) {
     const size_t head_off = (size_t)g * GL_PAGE * AD_HD;
     const size_t page_stride = (size_t)a.nKV * GL_PAGE * AD_HD;
 
-    for (int i = tid; i < G * AD_HD; i += AD_THREADS) {
-        const int h = g * G + i / AD_HD;
-        qs[i] = __bfloat162float(a.q[((size_t)b * a.nH + h) * AD_HD + (i % AD_HD)]);
-    }
-    float acc[GM][8];
-    float m_run[GM], l_run[GM];
+    // the queries as the 8-column operand: column = head within the group, rows = head dims
+    unsigned qb[AD_KS][2];
+    {
+        const __nv_bfloat16* qh = a.q + ((size_t)b * a.nH + (size_t)g * G + grp) * AD_HD;
 #pragma unroll
-    for (int q = 0; q < GM; ++q) {
-        m_run[q] = -INFINITY; l_run[q] = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[q][e] = 0.f;
+        for (int kk = 0; kk < AD_KS; ++kk) {
+            qb[kk][0] = grp < G ? *(const unsigned*)(qh + kk * 16 + 2 * t) : 0u;
+            qb[kk][1] = grp < G ? *(const unsigned*)(qh + kk * 16 + 8 + 2 * t) : 0u;
+        }
     }
-    const int my_chunk = tid % AD_CHUNKS, my_kg = tid / AD_CHUNKS;   // value pass: my 8 dims, my keys
-    const bool v_active = my_kg < AD_KG;
+    float o[AD_KS][4];                                   // [d tile][d g | g+8, head 2t | 2t+1]
+#pragma unroll
+    for (int i = 0; i < AD_KS; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // heads 2t, 2t+1; this warp's keys only
+    const float LOG2E = 1.4426950408889634f;
 
-    if (p_begin < p_end) {
-        load_page(Kt[0], a.k_cache + (size_t)pg[p_begin] * page_stride + head_off);
-        load_page(Vt[0], a.v_cache + (size_t)pg[p_begin] * page_stride + head_off);
+#pragma unroll
+    for (int s = 0; s < AD_STAGES - 1; ++s) {
+        const int p = p_begin + s;
+        if (p < p_end) {
+            const int nv = min(GL_PAGE, pos + 1 - p * GL_PAGE);
+            ad_load_page(sbase + 2 * s * AD_TILE, a.k_cache + (size_t)pg[p] * page_stride + head_off, nv);
+            ad_load_page(sbase + (2 * s + 1) * AD_TILE, a.v_cache + (size_t)pg[p] * page_stride + head_off, nv);
+        }
+        ad_commit();
     }
-    __pipeline_commit();
     for (int p = p_begin; p < p_end; ++p) {
-        const int st = (p - p_begin) & 1;
-        if (p + 1 < p_end) {
-            load_page(Kt[st ^ 1], a.k_cache + (size_t)pg[p + 1] * page_stride + head_off);
-            load_page(Vt[st ^ 1], a.v_cache + (size_t)pg[p + 1] * page_stride + head_off);
-        }
-        __pipeline_commit();
-        __pipeline_wait_prior(1);
-        __syncthreads();
-        const int j0 = p * GL_PAGE;
-        const int n_valid = min(GL_PAGE, pos + 1 - j0);          // rows past the sequence were never written
-        // scores: thread = (key, half of the head dims); the two halves meet by shuffle
+        const int st = (p - p_begin) % AD_STAGES;
+        ad_wait<AD_STAGES - 2>();
+        __syncthreads();                                 // page p has landed; the stage read last time is free
         {
-            const int key = tid >> 1, half = tid & 1;
-            const unsigned char* kr = Kt[st] + key * AD_ROW + half * AD_HD;   // hd/2 elements = hd bytes
-            const bool ok = key < n_valid && j0 + key >= lo;
-#pragma unroll
-            for (int q = 0; q < GM; ++q) {
-                if (q >= G) break;
-                float s = 0.f;
-                if (ok) {
-                    const float* qv = qs + q * AD_HD + half * (AD_HD / 2);
-#pragma unroll
-                    for (int c = 0; c < AD_HD / 16; ++c) {
-                        const uint4 raw = *(const uint4*)(kr + c * 16);
-                        const __nv_bfloat162* k2 = (const __nv_bfloat162*)&raw;
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 kf = __bfloat1622float2(k2[e]);
-                            s = fmaf(qv[c * 8 + 2 * e], kf.x, s);
-                            s = fmaf(qv[c * 8 + 2 * e + 1], kf.y, s);
-                        }
-                    }
-                }
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s = ok ? s : -INFINITY;
-                if (half == 0) ps[q * GL_PAGE + key] = s;
-                const float wm = gl_warp_max(s);
-                if (lane == 0) red[q * 8 + warp] = wm;
+            const int pn = p + AD_STAGES - 1, sn = (pn - p_begin) % AD_STAGES;
+            if (pn < p_end) {
+                const int nv = min(GL_PAGE, pos + 1 - pn * GL_PAGE);
+                ad_load_page(sbase + 2 * sn * AD_TILE, a.k_cache + (size_t)pg[pn] * page_stride + head_off, nv);
+                ad_load_page(sbase + (2 * sn + 1) * AD_TILE, a.v_cache + (size_t)pg[pn] * page_stride + head_off, nv);
             }
+            ad_commit();
         }
-        __syncthreads();
-        // running maximum and sum; weights replace scores
+        const unsigned Ks = sbase + 2 * st * AD_TILE, Vs = Ks + AD_TILE;
+        const int j0 = p * GL_PAGE + warp * 16;          // this warp's first key
+        if (j0 > pos) continue;                          // all of this warp's keys lie past the sequence
+        // scores: [16 keys] x [8 heads]
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int q = 0; q < GM; ++q) {
-            if (q >= G) break;
-            const float pm = fmaxf(fmaxf(red[q * 8], red[q * 8 + 1]), fmaxf(red[q * 8 + 2], red[q * 8 + 3]));
-            const float m_new = fmaxf(m_run[q], pm);
-            const float corr = (m_new == -INFINITY) ? 1.f : __expf(m_run[q] - m_new);
-            float w = 0.f;
-            if (tid < GL_PAGE) {
-                const float s = ps[q * GL_PAGE + tid];
-                w = (s == -INFINITY) ? 0.f : __expf(s - m_new);
-                ps[q * GL_PAGE + tid] = w;
-            }
-            const float ws = gl_warp_sum(w);
-            if (lane == 0) red[q * 8 + 4 + warp] = ws;
-            m_run[q] = m_new;
-            l_run[q] *= corr;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[q][e] *= corr;
+        for (int kk = 0; kk < AD_KS; ++kk) {
+            unsigned af[4];
+            const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int c = kk * 2 + (lane >> 4);
+            ad_ldm4(Ks + r * AD_ROW + c * 16, af);
+            ad_mma(s4, af, qb[kk][0], qb[kk][1]);
         }
-        __syncthreads();
-#pragma unroll
-        for (int q = 0; q < GM; ++q)
-            if (q < G) l_run[q] += red[q * 8 + 4] + red[q * 8 + 5];           // only warps 0 and 1 hold keys
-        // values: thread = (8 dims, every AD_KG-th key)
-        if (v_active) {
-            for (int j = my_kg; j < n_valid; j += AD_KG) {
-                const uint4 raw = *(const uint4*)(Vt[st] + j * AD_ROW + my_chunk * 16);
-                const __nv_bfloat162* v2 = (const __nv_bfloat162*)&raw;
-                float vf[8];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = __bfloat1622float2(v2[e]);
-                    vf[2 * e] = f.x; vf[2 * e + 1] = f.y;
-                }
-#pragma unroll
-                for (int q = 0; q < GM; ++q) {
-                    if (q >= G) break;
-                    const float w = ps[q * GL_PAGE + j];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[q][e] = fmaf(w, vf[e], acc[q][e]);
-                }
-            }
+        {
+            const int k_lo = j0 + grp, k_hi = k_lo + 8;
+            if (k_lo > pos || k_lo < lo) { s4[0] = -INFINITY; s4[1] = -INFINITY; }
+            if (k_hi > pos || k_hi < lo) { s4[2] = -INFINITY; s4[3] = -INFINITY; }
         }
-        __syncthreads();
+        float mx[2] = {fmaxf(s4[0], s4[2]), fmaxf(s4[1], s4[3])};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 4));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 8));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 16));
+        }
+        float corr[2], mu[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float m_new = fmaxf(m_run[i], mx[i]);
+            mu[i] = (m_new == -INFINITY) ? 0.f : m_new * LOG2E;
+            corr[i] = exp2f(m_run[i] * LOG2E - mu[i]);    // m_run = -inf gives 0
+            m_run[i] = m_new;
+        }
+        const float p0 = exp2f(s4[0] * LOG2E - mu[0]), p1 = exp2f(s4[1] * LOG2E - mu[1]);
+        const float p2 = exp2f(s4[2] * LOG2E - mu[0]), p3 = exp2f(s4[3] * LOG2E - mu[1]);
+        l_run[0] = l_run[0] * corr[0] + p0 + p2;         // summed over the 8 key lanes at the end
+        l_run[1] = l_run[1] * corr[1] + p1 + p3;
+        // weights to the 8-column operand layout: through this warp's [head][key] corner of shared memory
+        __nv_bfloat16* pm = pw + warp * 128;
+        __syncwarp();
+        pm[(2 * t) * 16 + grp] = __float2bfloat16_rn(p0);
+        pm[(2 * t + 1) * 16 + grp] = __float2bfloat16_rn(p1);
+        pm[(2 * t) * 16 + grp + 8] = __float2bfloat16_rn(p2);
+        pm[(2 * t + 1) * 16 + grp + 8] = __float2bfloat16_rn(p3);
+        __syncwarp();
+        const unsigned pb0 = *(const unsigned*)(pm + grp * 16 + 2 * t);
+        const unsigned pb1 = *(const unsigned*)(pm + grp * 16 + 8 + 2 * t);
+#pragma unroll
+        for (int dt = 0; dt < AD_KS; ++dt) {
+            o[dt][0] *= corr[0]; o[dt][1] *= corr[1]; o[dt][2] *= corr[0]; o[dt][3] *= corr[1];
+            unsigned vf[4];
+            const int r = warp * 16 + (lane >> 4) * 8 + (lane & 7);
+            const int c = dt * 2 + ((lane >> 3) & 1);
+            ad_ldm4t(Vs + r * AD_ROW + c * 16, vf);
+            ad_mma(o[dt], vf, pb0, pb1);
+        }
     }
-    __pipeline_wait_prior(0);
-
-    // sum the key groups, one query head at a time, and write the split's result
+    ad_wait<0>();
+    // the sums over this warp's key lanes
 #pragma unroll
-    for (int q = 0; q < GM; ++q) {
-        if (q >= G) break;
-        __syncthreads();
-        if (v_active) {
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 4);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 8);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 16);
+    }
+    // merge the four warps: (max, sum) per head, then the outputs rescaled to the common maximum
+    float* ml_w = mrg;                                   // [4][8][2]
+    float* o_w = mrg + 64;                               // [4][hd][G]
+    __syncthreads();
+    if (grp == 0) {
+        ml_w[(warp * 8 + 2 * t) * 2] = m_run[0];     ml_w[(warp * 8 + 2 * t) * 2 + 1] = l_run[0];
+        ml_w[(warp * 8 + 2 * t + 1) * 2] = m_run[1]; ml_w[(warp * 8 + 2 * t + 1) * 2 + 1] = l_run[1];
+    }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) osum[my_kg * AD_HD + my_chunk * 8 + e] = acc[q][e];
+    for (int dt = 0; dt < AD_KS; ++dt) {
+        float* ow = o_w + ((size_t)warp * AD_HD + dt * 16 + grp) * G + 2 * t;
+        if (2 * t < G) { ow[0] = o[dt][0]; ow[8 * G] = o[dt][2]; }             // d and d + 8
+        if (2 * t + 1 < G) { ow[1] = o[dt][1]; ow[8 * G + 1] = o[dt][3]; }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * AD_HD; i += AD_THREADS) {
+        const int hq = i / AD_HD, d = i - hq * AD_HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_w[(w * 8 + hq) * 2]);
+        float ov = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = ml_w[(w * 8 + hq) * 2];
+            if (mw == -INFINITY) continue;
+            const float f = exp2f((mw - m) * LOG2E);
+            ov = fmaf(f, o_w[((size_t)w * AD_HD + d) * G + hq], ov);
+            l = fmaf(f, ml_w[(w * 8 + hq) * 2 + 1], l);
         }
-        __syncthreads();
-        const int h = g * G + q;
-        for (int d = tid; d < AD_HD; d += AD_THREADS) {
-            float o = 0.f;
-            for (int kg = 0; kg < AD_KG; ++kg) o += osum[kg * AD_HD + d];
-            if (a.splits == 1) {
-                const float inv = l_run[q] > 0.f ? 1.f / l_run[q] : 0.f;
-                a.out[((size_t)b * a.nH + h) * AD_HD + d] = __float2bfloat16_rn(o * inv);
-            } else {
-                a.part_o[(((size_t)b * a.nH + h) * a.splits + split) * AD_HD + d] = o;
+        const int h = g * G + hq;
+        if (a.splits == 1) {
+            a.out[((size_t)b * a.nH + h) * AD_HD + d] = __float2bfloat16_rn(l > 0.f ? ov / l : 0.f);
+        } else {
+            a.part_o[(((size_t)b * a.nH + h) * a.splits + split) * AD_HD + d] = ov;
+            if (d == 0) {
+                float* ml = a.part_ml + (((size_t)b * a.nH + h) * a.splits + split) * 2;
+                ml[0] = m;
+                ml[1] = l;
             }
-        }
-        if (a.splits > 1 && tid == 0) {
-            float* ml = a.part_ml + (((size_t)b * a.nH + h) * a.splits + split) * 2;
-            ml[0] = m_run[q];
-            ml[1] = l_run[q];
         }
     }
 }
@@ -221,7 +262,7 @@ __global__ void attn_decode_merge_kernel(DecodeArgs a) {
         for (int s = 0; s < a.splits; ++s) {
             const float ms = ml[2 * s];
             if (ms == -INFINITY) continue;
-            const float w = __expf(ms - m);
+            const float w = exp2f((ms - m) * 1.4426950408889634f);
             o = fmaf(w, po[s * AD_HD + d], o);
             l = fmaf(w, ml[2 * s + 1], l);
         }
@@ -229,23 +270,22 @@ __global__ void attn_decode_merge_kernel(DecodeArgs a) {
     }
 }
 
-static size_t decode_smem(int gm) {
-    return 4 * (size_t)AD_TILE + sizeof(float) * ((size_t)gm * AD_HD + gm * GL_PAGE + gm * 8 + (size_t)AD_KG * AD_HD);
+static size_t decode_smem(int G) {
+    return 2 * AD_STAGES * (size_t)AD_TILE + 4 * 8 * 16 * 2 + sizeof(float) * (64 + 4 * (size_t)AD_HD * G);
 }
 
-template <int GM>
 static int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     static bool configured = false;
-    const size_t smem = decode_smem(GM);
+    const size_t smem = decode_smem(a.nH / a.nKV);
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_decode_kernel<GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(AD_MAXG)) != cudaSuccess) {
             cudaGetLastError();
             return GL_ERR_SMEM;
         }
         configured = true;
     }
     dim3 grid(a.splits, a.nKV, a.B);
-    attn_decode_kernel<GM><<<grid, AD_THREADS, smem, stream>>>(a);
+    attn_decode_kernel<<<grid, AD_THREADS, smem, stream>>>(a);
     return GL_OK;
 }
 
@@ -262,12 +302,7 @@ GL_API int gl_attention_decode(const DecodeArgs* args, cudaStream_t stream) {
     if (a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV || a.nH / a.nKV > AD_MAXG) return GL_ERR_SHAPE;
     if (a.splits < 1 || a.B > 65535 || a.nKV > 65535) return GL_ERR_SHAPE;
     if (a.splits > 1 && (!a.part_o || !a.part_ml)) return GL_ERR_SHAPE;
-    const int G = a.nH / a.nKV;
-    int rc;
-    if (G == 1) rc = launch_decode<1>(a, stream);
-    else if (G == 2) rc = launch_decode<2>(a, stream);
-    else if (G <= 4) rc = launch_decode<4>(a, stream);
-    else rc = launch_decode<8>(a, stream);
+    const int rc = launch_decode(a, stream);
     if (rc != GL_OK) return rc;
     if (a.splits > 1) {
         dim3 mg(a.nH, a.B);

@@ -289,9 +289,8 @@ def sm_count(device) -> int:
 
 def decode_blocks_per_sm(head_dim: int, group: int = 1) -> int:
     """Blocks of the decode kernel one SM holds at once (bounded by shared memory)."""
-    gm = 1 if group <= 1 else 2 if group == 2 else 4 if group <= 4 else 8
-    kg = 128 // (head_dim // 8)
-    smem = 4 * PAGE * (2 * head_dim + 16) + 4 * (gm * head_dim + gm * PAGE + gm * 8 + kg * head_dim)
+    stages = 2
+    smem = 2 * stages * PAGE * (2 * head_dim + 16) + 1024 + 4 * (64 + 4 * head_dim * max(1, group))
     return max(1, min(8, (227 * 1024) // (smem + 1024)))
 
 
