@@ -10,11 +10,14 @@
 // weighted values are a second chain (values transposed by ldmatrix as the 16-row
 // operand) into 32-bit accumulators.  The warps never wait for one another inside
 // the loop except at the barrier that hands a page buffer back; their four partial
-// softmaxes are merged at the end.  Splits write (max, sum, unnormalised output)
-// to scratch and a second kernel merges them; with one split the block writes the
-// result itself.  The head size is a compile-time constant (GL_HEAD_DIM, a
+// softmaxes are merged at the end.  With one split the block writes the result
+// itself.  Up to 8 splits form a thread-block cluster and merge through distributed
+// shared memory; more splits (or a caller that passes scratch) write (max, sum,
+// unnormalised output) to scratch and a second kernel merges them.  The head size is a compile-time constant (GL_HEAD_DIM, a
 // multiple of 16).
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 #ifndef GL_HEAD_DIM
 #define GL_HEAD_DIM 80
@@ -79,6 +82,8 @@ __device__ __forceinline__ void ad_load_page(unsigned dst, const __nv_bfloat16* 
     }
 }
 
+// CLUSTER: the splits of one (sequence, key/value head) are the blocks of a cluster
+template <bool CLUSTER>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(DecodeArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -90,6 +95,8 @@ attn_decode_kernel(DecodeArgs a) {
     const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = lane >> 2, t = lane & 3;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
     const int G = a.nH / a.nKV;                          // query heads of this key/value head (<= 8)
     const int pos = a.seq_ctx[b];                        // the query's position; keys lo..pos
     const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
@@ -210,6 +217,8 @@ attn_decode_kernel(DecodeArgs a) {
     // merge the four warps: (max, sum) per head, then the outputs rescaled to the common maximum
     float* ml_w = mrg;                                   // [4][8][2]
     float* o_w = mrg + 64;                               // [4][hd][G]
+    float* fin_o = o_w + 4 * AD_HD * G;                  // [G][hd] this split's result, for the cluster merge
+    float* fin_ml = fin_o + G * AD_HD;                   // [G][2]
     __syncthreads();
     if (grp == 0) {
         ml_w[(warp * 8 + 2 * t) * 2] = m_run[0];     ml_w[(warp * 8 + 2 * t) * 2 + 1] = l_run[0];
@@ -239,6 +248,9 @@ attn_decode_kernel(DecodeArgs a) {
         const int h = g * G + hq;
         if (a.splits == 1) {
             a.out[((size_t)b * a.nH + h) * AD_HD + d] = __float2bfloat16_rn(l > 0.f ? ov / l : 0.f);
+        } else if (CLUSTER) {
+            fin_o[i] = ov;
+            if (d == 0) { fin_ml[2 * hq] = m; fin_ml[2 * hq + 1] = l; }
         } else {
             a.part_o[(((size_t)b * a.nH + h) * a.splits + split) * AD_HD + d] = ov;
             if (d == 0) {
@@ -248,11 +260,35 @@ attn_decode_kernel(DecodeArgs a) {
             }
         }
     }
+    if (CLUSTER) {
+        // the splits meet in distributed shared memory; block r finishes every S-th output, in rank order
+        cg::cluster_group cluster = cg::this_cluster();
+        const int S = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+        cluster.sync();
+        for (int i = tid * S + rank; i < G * AD_HD; i += AD_THREADS * S) {
+            const int hq = i / AD_HD, d = i - hq * AD_HD;
+            float m = -INFINITY;
+            for (int s = 0; s < S; ++s) m = fmaxf(m, cluster.map_shared_rank(fin_ml, s)[2 * hq]);
+            float ov = 0.f, l = 0.f;
+            for (int s = 0; s < S; ++s) {
+                const float* pml = cluster.map_shared_rank(fin_ml, s);
+                const float ms = pml[2 * hq];
+                if (ms == -INFINITY) continue;
+                const float f = exp2f((ms - m) * LOG2E);
+                ov = fmaf(f, cluster.map_shared_rank(fin_o, s)[i], ov);
+                l = fmaf(f, pml[2 * hq + 1], l);
+            }
+            a.out[((size_t)b * a.nH + g * G + hq) * AD_HD + d] = __float2bfloat16_rn(l > 0.f ? ov / l : 0.f);
+        }
+        cluster.sync();
+    }
 }
 
 // out = sum_s exp(m_s - m) o_s / sum_s exp(m_s - m) l_s over the splits, in split order
 __global__ void attn_decode_merge_kernel(DecodeArgs a) {
     const int h = blockIdx.x, b = blockIdx.y;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
     const float* ml = a.part_ml + ((size_t)b * a.nH + h) * a.splits * 2;
     const float* po = a.part_o + ((size_t)b * a.nH + h) * a.splits * AD_HD;
     float m = -INFINITY;
@@ -271,22 +307,24 @@ __global__ void attn_decode_merge_kernel(DecodeArgs a) {
 }
 
 static size_t decode_smem(int G) {
-    return 2 * AD_STAGES * (size_t)AD_TILE + 4 * 8 * 16 * 2 + sizeof(float) * (64 + 4 * (size_t)AD_HD * G);
+    return 2 * AD_STAGES * (size_t)AD_TILE + 4 * 8 * 16 * 2 + sizeof(float) * (64 + 5 * (size_t)AD_HD * G + 2 * G);
 }
 
 static int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = decode_smem(a.nH / a.nKV);
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(AD_MAXG)) != cudaSuccess) {
+        if (cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(AD_MAXG)) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(AD_MAXG)) != cudaSuccess) {
             cudaGetLastError();
             return GL_ERR_SMEM;
         }
         configured = true;
     }
-    dim3 grid(a.splits, a.nKV, a.B);
-    attn_decode_kernel<<<grid, AD_THREADS, smem, stream>>>(a);
-    return GL_OK;
+    const dim3 grid(a.splits, a.nKV, a.B);
+    if (a.splits > 1 && a.splits <= 8 && !a.part_o)
+        return gl_launch(attn_decode_kernel<true>, grid, dim3(AD_THREADS), smem, stream, a.splits, a);
+    return gl_launch(attn_decode_kernel<false>, grid, dim3(AD_THREADS), smem, stream, 1, a);
 }
 
 GL_API int gl_attention_decode_head_dim() { return AD_HD; }
@@ -301,14 +339,14 @@ GL_API int gl_attention_decode(const DecodeArgs* args, cudaStream_t stream) {
     if (a.B <= 0) return GL_OK;
     if (a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV || a.nH / a.nKV > AD_MAXG) return GL_ERR_SHAPE;
     if (a.splits < 1 || a.B > 65535 || a.nKV > 65535) return GL_ERR_SHAPE;
-    if (a.splits > 1 && (!a.part_o || !a.part_ml)) return GL_ERR_SHAPE;
+    if (a.splits > 8 && (!a.part_o || !a.part_ml)) return GL_ERR_SHAPE;     // more than a cluster holds: scratch
+    if ((a.part_o == nullptr) != (a.part_ml == nullptr)) return GL_ERR_SHAPE;
     const int rc = launch_decode(a, stream);
     if (rc != GL_OK) return rc;
-    if (a.splits > 1) {
-        dim3 mg(a.nH, a.B);
-        attn_decode_merge_kernel<<<mg, AD_HD >= 128 ? 128 : 64, 0, stream>>>(a);
+    if (a.splits > 1 && a.part_o) {
+        return gl_launch(attn_decode_merge_kernel, dim3(a.nH, a.B), dim3(AD_HD >= 128 ? 128 : 64), 0, stream, 1, a);
     }
-    return gl_check_launch();
+    return GL_OK;
 }
 
 // ---------------------------------------------------------------------------

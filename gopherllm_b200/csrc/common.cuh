@@ -32,6 +32,52 @@ enum GlError {
 // tokens of the cache that share one page
 #define GL_PAGE 64
 
+// Programmatic dependent launch.  A kernel launched through gl_launch may begin while the
+// kernel before it in the stream is still finishing: blocks are scheduled and run up to
+// gl_grid_wait(), which returns once every kernel it depends on has completed and its writes
+// are visible.  Everything a kernel reads from or writes to memory that an earlier kernel
+// touches must therefore come after gl_grid_wait(); only constants of the launch (weights,
+// barrier set-up) may come before.  gl_grid_launch_dependents() lets the next kernel start
+// being scheduled.  Both are no-ops in a kernel launched the ordinary way.
+static int gl_pdl = 1;
+GL_API void gl_set_pdl(int on) { gl_pdl = on; }
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void gl_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gl_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static int gl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                     int cluster_x, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (gl_pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    if (cudaLaunchKernelEx(&cfg, kernel, args...) != cudaSuccess) {
+        cudaGetLastError();
+        return -4;
+    }
+    return 0;
+}
+#endif
+
 static inline int gl_check_launch() {
     return cudaGetLastError() == cudaSuccess ? GL_OK : GL_ERR_LAUNCH;
 }

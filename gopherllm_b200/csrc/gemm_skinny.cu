@@ -73,10 +73,13 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
         mbar_fence_init();
     }
     __syncthreads();
-    auto load_stage = [&](int it) {                           // one thread
+    auto load_w = [&](int it) {                               // one thread: the stage's weights
         const unsigned sb = base + (it % STAGES) * STAGE, bar = bars + 8 * (it % STAGES);
-        mbar_expect_tx(bar, STAGE);
+        mbar_expect_tx(bar, STAGE);                           // the activations of the stage count too
         tma_load_2d(sb, &map_w, kb + it * SK_BK, n0, bar);
+    };
+    auto load_a = [&](int it) {                               // one thread: the stage's activations
+        const unsigned sb = base + (it % STAGES) * STAGE, bar = bars + 8 * (it % STAGES);
         tma_load_2d(sb + W_BYTES, &map_a, kb + it * SK_BK, 0, bar);
     };
 
@@ -86,12 +89,18 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[mt][e] = 0.f;
 
+    // The weights do not depend on the kernel before this one: their first stages are under way
+    // before this kernel waits for it.  The activations and everything written come after.
+    gl_grid_launch_dependents();
     if (tid == 0)
-        for (int s = 0; s < STAGES - 1 && s < iters; ++s) load_stage(s);
+        for (int s = 0; s < STAGES - 1 && s < iters; ++s) load_w(s);
+    gl_grid_wait();
+    if (tid == 0)
+        for (int s = 0; s < STAGES - 1 && s < iters; ++s) load_a(s);
     for (int it = 0; it < iters; ++it) {
         if (!mbar_wait(bars + 8 * (it % STAGES), (it / STAGES) & 1)) break;
         __syncthreads();                                      // everyone is done with the stage refilled next
-        if (tid == 0 && it + STAGES - 1 < iters) load_stage(it + STAGES - 1);
+        if (tid == 0 && it + STAGES - 1 < iters) { load_w(it + STAGES - 1); load_a(it + STAGES - 1); }
         const unsigned sb = base + (it % STAGES) * STAGE;
 #pragma unroll
         for (int kk = 0; kk < SK_BK / 16; ++kk) {
@@ -173,23 +182,10 @@ static int launch_skinny(const GemmArgs& g, int S, cudaStream_t stream) {
     if (rc != GL_OK) return rc;
     rc = gl_cached_map_bf16(&map_a, g.a, (uint64_t)g.M, (uint64_t)g.K, MT * 8, SK_BK);
     if (rc != GL_OK) return rc;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(S, (g.N + SK_ROWS - 1) / SK_ROWS, 1);
-    cfg.blockDim = dim3(SK_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = S;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    if (cfg.gridDim.y > 65535) return GL_ERR_SHAPE;
-    if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<MT, STAGES, TO>, g, k_per_block, map_w, map_a) != cudaSuccess) {
-        cudaGetLastError();
+    const dim3 grid(S, (g.N + SK_ROWS - 1) / SK_ROWS, 1);
+    if (grid.y > 65535) return GL_ERR_SHAPE;
+    if (gl_launch(gemm_skinny_kernel<MT, STAGES, TO>, grid, dim3(SK_THREADS), smem, stream, S, g, k_per_block, map_w, map_a) != 0)
         return GL_ERR_LAUNCH;
-    }
     return GL_OK;
 }
 

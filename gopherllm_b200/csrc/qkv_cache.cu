@@ -12,6 +12,8 @@
 __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
                                   float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
     if (i >= T * half) return;
     const int t = i / half, p = i % half;
     const float a = (float)pos[t] * inv_freq[p];
@@ -25,8 +27,7 @@ GL_API int gl_rope_table(const int* pos, const float* inv_freq, float* cosv, flo
                          int T, int half, cudaStream_t stream) {
     if (T <= 0 || half <= 0) return GL_OK;
     const int n = T * half;
-    rope_table_kernel<<<(n + 127) / 128, 128, 0, stream>>>(pos, inv_freq, cosv, sinv, T, half);
-    return gl_check_launch();
+    return gl_launch(rope_table_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 1, pos, inv_freq, cosv, sinv, T, half);
 }
 
 struct QkvCacheArgs {
@@ -51,6 +52,8 @@ struct QkvCacheArgs {
 template <typename TA, typename TC>
 __global__ void qkv_cache_kernel(QkvCacheArgs a) {
     extern __shared__ float smem[];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = a.nH + 2 * a.nKV;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
@@ -118,15 +121,11 @@ GL_API int gl_qkv_cache(const QkvCacheArgs* args, int act_dtype, int cache_dtype
     const long long items = (long long)a.T * (a.nH + 2 * a.nKV);
     const unsigned blocks = (unsigned)((items + warps - 1) / warps);
     const size_t smem = (size_t)warps * a.hd * sizeof(float);
-    if (act_dtype == GL_F32 && cache_dtype == GL_F32)
-        qkv_cache_kernel<float, float><<<blocks, warps * 32, smem, stream>>>(a);
-    else if (act_dtype == GL_BF16 && cache_dtype == GL_BF16)
-        qkv_cache_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(a);
-    else if (act_dtype == GL_BF16 && cache_dtype == GL_F32)
-        qkv_cache_kernel<__nv_bfloat16, float><<<blocks, warps * 32, smem, stream>>>(a);
-    else if (act_dtype == GL_F32 && cache_dtype == GL_BF16)
-        qkv_cache_kernel<float, __nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(a);
-    else
-        return GL_ERR_DTYPE;
-    return gl_check_launch();
+    const dim3 g(blocks), b(warps * 32);
+    if (act_dtype == GL_F32 && cache_dtype == GL_F32) return gl_launch(qkv_cache_kernel<float, float>, g, b, smem, stream, 1, a);
+    if (act_dtype == GL_BF16 && cache_dtype == GL_BF16)
+        return gl_launch(qkv_cache_kernel<__nv_bfloat16, __nv_bfloat16>, g, b, smem, stream, 1, a);
+    if (act_dtype == GL_BF16 && cache_dtype == GL_F32) return gl_launch(qkv_cache_kernel<__nv_bfloat16, float>, g, b, smem, stream, 1, a);
+    if (act_dtype == GL_F32 && cache_dtype == GL_BF16) return gl_launch(qkv_cache_kernel<float, __nv_bfloat16>, g, b, smem, stream, 1, a);
+    return GL_ERR_DTYPE;
 }

@@ -115,6 +115,8 @@ sample_kernel(SampleArgs a) {
     __shared__ int s_found;
 
     const int b = blockIdx.x, tid = threadIdx.x, V = a.V;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
     const int row = a.state_row ? a.state_row[b] : b;
     const float* src = a.logits + (size_t)b * V;
     float* w = a.work + (size_t)b * V;
@@ -341,6 +343,5 @@ GL_API int gl_sample(const SampleArgs* args, cudaStream_t stream) {
         const bool whole_row = !(a.top_k > 0 && a.top_k < a.V);
         if (whole_row && (a.top_p < 1.0f || a.min_p > 0.f)) return GL_ERR_SHAPE;
     }
-    sample_kernel<<<a.B, SM_THREADS, 0, stream>>>(a);
-    return gl_check_launch();
+    return gl_launch(sample_kernel, dim3(a.B), dim3(SM_THREADS), 0, stream, 1, a);
 }

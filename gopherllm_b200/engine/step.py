@@ -42,6 +42,7 @@ class StepContext:
         self.n_tokens = self.n_seqs = self.n_want = 0
         self.max_qlen = self.max_len = 0
         self.is_decode = False
+        self.side_stream = None          # a second stream blocks may fork onto (decode steps only)
 
 
 def _pad4(n: int) -> int:
@@ -81,6 +82,8 @@ class Engine:
         self.graph_max_batch = 256
         self._graphs: Dict[tuple, object] = {}
         self._graph_pool = None
+        self.overlap_branches = True                         # decode steps run parallel branches on two streams
+        self._side_stream = None
         self.launches_per_loop_step: Dict[int, int] = {}    # kernels in one captured decode_loop step, by batch
         self._pinned: List[Optional[torch.Tensor]] = [None, None]
         self._events: List[Optional[torch.cuda.Event]] = [None, None]
@@ -179,6 +182,10 @@ class Engine:
         ctx.n_tokens, ctx.n_seqs, ctx.n_want = lay.T, lay.B, lay.M
         ctx.max_qlen, ctx.is_decode = meta["max_qlen"], meta["is_decode"]
         ctx.max_len = max(meta["new_lens"])
+        if ctx.is_decode and self.overlap_branches and self.act_dtype == torch.bfloat16:
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=self.device)
+            ctx.side_stream = self._side_stream
         return ctx
 
     @torch.no_grad()

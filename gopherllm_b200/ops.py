@@ -290,7 +290,7 @@ def sm_count(device) -> int:
 def decode_blocks_per_sm(head_dim: int, group: int = 1) -> int:
     """Blocks of the decode kernel one SM holds at once (bounded by shared memory)."""
     stages = 2
-    smem = 2 * stages * PAGE * (2 * head_dim + 16) + 1024 + 4 * (64 + 4 * head_dim * max(1, group))
+    smem = 2 * stages * PAGE * (2 * head_dim + 16) + 1024 + 4 * (64 + 5 * head_dim * max(1, group) + 16)
     return max(1, min(8, (227 * 1024) // (smem + 1024)))
 
 
@@ -301,15 +301,16 @@ def decode_splits(batch: int, num_kv_heads: int, max_len: int, device, head_dim:
     nearly empty wave), never more than the longest sequence has pages."""
     pages = max(1, -(-max_len // PAGE))
     slots = sm_count(device) * decode_blocks_per_sm(head_dim, group)
-    return max(1, min(slots // max(1, batch * num_kv_heads), pages, 64))
+    return max(1, min(slots // max(1, batch * num_kv_heads), pages, 8))
 
 
 def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, num_kv_heads: int,
                      head_dim: int, splits: int, window: int = 0,
                      scratch: Optional[torch.Tensor] = None) -> None:
     """One query per sequence (row b of q is sequence b) over the bfloat16 cache.
-    ``scratch`` (float32, at least B*nH*splits*(hd+2) elements) holds the splits' partial
-    results; it is allocated when not given."""
+    Up to 8 splits merge inside a thread-block cluster and need no scratch.  More splits, or
+    ``scratch`` given (float32, at least B*nH*splits*(hd+2) elements), write partial results
+    to scratch (allocated here when needed and not given) for a second kernel to merge."""
     B = q.shape[0]
     _need(q, "q", torch.bfloat16, (B, num_heads * head_dim))
     _need(out, "out", torch.bfloat16, q.shape)
@@ -327,7 +328,7 @@ def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, n
         raise KernelError(f"decode attention takes up to {DECODE_MAX_GROUP} query heads per key/value head")
     lib = _lib("attention_decode.cu", catalog.head_dim_defines(head_dim))
     part_o = part_ml = None
-    if splits > 1:
+    if splits > 8 or (splits > 1 and scratch is not None):
         n_o, n_ml = B * num_heads * splits * head_dim, B * num_heads * splits * 2
         if scratch is None:
             scratch = torch.empty(n_o + n_ml, dtype=torch.float32, device=q.device)
@@ -338,7 +339,7 @@ def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, n
     a = _DecodeArgs(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                     seq_ctx.data_ptr(), pages.data_ptr(), part_o, part_ml,
                     B, num_heads, num_kv_heads, pages.shape[-1], window, splits)
-    _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode", 2 if splits > 1 else 1)
+    _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode", 2 if part_o is not None else 1)
 
 
 def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads: int,
@@ -513,6 +514,15 @@ def sample(logits: torch.Tensor, work: torch.Tensor, recent: torch.Tensor, recen
                     recent_n.data_ptr(), rng.data_ptr(), out.data_ptr(), B, V, top_k,
                     temperature, top_p, min_p, repeat_penalty)
     _check(_lib("sampling.cu").gl_sample(byref(a), _stream()), "sample")
+
+
+def set_pdl(on: bool) -> None:
+    """Switch programmatic dependent launch on or off in every library loaded so far (on by
+    default).  With it a kernel's blocks may be scheduled, and a product may start fetching
+    its weights, while the kernel before it is still finishing."""
+    for lib in list(build._loaded.values()):
+        if hasattr(lib, "gl_set_pdl"):
+            lib.gl_set_pdl(c_int(1 if on else 0))
 
 
 def warm_up(head_dims=()) -> None:

@@ -49,8 +49,26 @@ class ParallelBlock(_AssembledBlock):
     def forward(self, x, ctx, cache):
         xn = self.norm.forward(x, ctx.act_dtype)
         a = torch.empty_like(x)
+        side = getattr(ctx, "side_stream", None)
+        if side is None or not hasattr(self.ffn, "begin"):
+            self.mixer.forward(xn, ctx, cache, (), a)
+            self.ffn.forward(xn, ctx, (x, a), x)
+            return x
+        # Both branches read the same normalised input, so the feed-forward's first half runs
+        # on a second stream beside the mixer: with few tokens every kernel is a stream of
+        # weights, and the second stream keeps memory busy while the mixer's small kernels
+        # start and finish.  The branches meet before the second half, which adds them up.
+        main = torch.cuda.current_stream()
+        h = torch.empty(self.ffn.hidden_shape(x.shape[0]), dtype=ctx.act_dtype, device=x.device)
+        fork, join = torch.cuda.Event(), torch.cuda.Event()
+        fork.record(main)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            self.ffn.begin(xn, ctx, out=h)
+            join.record(side)
         self.mixer.forward(xn, ctx, cache, (), a)
-        self.ffn.forward(xn, ctx, (x, a), x)
+        main.wait_event(join)
+        self.ffn.finish(h, ctx, (x, a), x)
         return x
 
 

@@ -249,9 +249,10 @@ def test_attention_decode(nH, nKV, hd, window):
     kc, vc, table = make_cache(k, v, lens, dtype, seed=3)
     q = (rnd(B, nH, hd, seed=3) / math.sqrt(hd)).to(dtype)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
-    for splits in (1, 2, 5, 16):
+    for splits, scratch in ((1, None), (2, None), (5, None), (8, None), (16, None), (3, torch.empty(B * nH * 3 * (hd + 2), device=DEV))):
         out = torch.empty(B, nH * hd, dtype=dtype, device=DEV)
-        o.attention_decode(q.reshape(B, nH * hd), out, kc, vc, i32(ctxs), table, nH, nKV, hd, splits, window)
+        o.attention_decode(q.reshape(B, nH * hd), out, kc, vc, i32(ctxs), table, nH, nKV, hd, splits, window,
+                           scratch=scratch)
         for b in range(B):
             ref = ref_attention(q[b:b + 1].double().cpu(), k[b, :lens[b]].double().cpu(),
                                 v[b, :lens[b]].double().cpu(), ctxs[b], 1, window)
