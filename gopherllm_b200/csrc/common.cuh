@@ -101,6 +101,21 @@ __device__ __forceinline__ float gl_warp_max(float v) {
 // Activations in 32-bit.  gelu "tanh form" is x*sigmoid(2*sqrt(2/pi)*(x+0.044715x^3)),
 // the form the reference evaluates (fastmath.go:138-141); the erf form is
 // 0.5*x*(1+erf(x/sqrt(2))) (bert.go:742-744).
+// For results that are rounded to bfloat16 right away: the tanh form through the hardware's
+// tanh.approx (relative error about 2^-11, below bfloat16's 2^-9 rounding).
+__device__ __forceinline__ float gl_activate_bf16_grade(float x, int act) {
+    if (act == GL_ACT_GELU_TANH) {
+        float th;
+        const float u = 0.7978845608028654f * x * fmaf(0.044715f * x, x, 1.0f);
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(u));
+        const float hx = 0.5f * x;
+        return fmaf(hx, th, hx);
+    }
+    if (act == GL_ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    if (act == GL_ACT_RELU) return fmaxf(x, 0.0f);
+    return x;
+}
+
 template <bool EXACT>
 __device__ __forceinline__ float gl_activate(float x, int act) {
     switch (act) {

@@ -8,7 +8,11 @@
 // stages back through tcgen05.commit; warps 2..5 read a finished accumulator out
 // of tensor memory (tcgen05.ld, one row per thread), apply bias, activation and
 // the residual additions in 32-bit and store.  Two accumulators alternate, so the
-// epilogue of one tile runs under the products of the next.  Rows and columns
+// epilogue of one tile runs under the products of the next; to stay under them it must
+// not wait on memory or queue behind the operand traffic, so the bias of a tile is fetched
+// before its accumulator is ready and results leave by TMA from a swizzled patch in shared
+// memory: a plain tile store, or, for a product that is added onto its own output (out =
+// out + product, the residual stream), TMA's add-reduction, which loads nothing.  Rows and columns
 // outside the matrices are zero-filled by TMA and masked at the store.
 //
 // Every wait on an mbarrier is bounded; if one runs out the block records it,
@@ -69,16 +73,17 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
 
 template <int BN, int STAGES, typename TO>
 __global__ void __launch_bounds__(TG_THREADS, 1)
-gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w) {
+gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_out, int out_mode) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int A_BYTES = TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
-    constexpr unsigned TMEM_COLS = 2 * BN >= 32 ? 2 * BN : 32;     // a power of two: BN is 64, 128 or 256
+    constexpr unsigned TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);   // a power of two holding both accumulators
     __shared__ unsigned tmem_base_slot;
     __shared__ volatile int failed;
 
     unsigned char* smem = smem_raw + ((1024u - (gl_smem_u32(smem_raw) & 1023u)) & 1023u);
     const unsigned base = gl_smem_u32(smem);
-    const unsigned bar_full = base + STAGES * STAGE;          // [STAGES]
+    const unsigned bar_full = base + STAGES * STAGE;          // [STAGES]; the barriers own 1024 bytes
     const unsigned bar_empty = bar_full + 8 * STAGES;         // [STAGES]
     const unsigned bar_tfull = bar_empty + 8 * STAGES;        // [2] accumulator ready for the epilogue
     const unsigned bar_tempty = bar_tfull + 16;               // [2] accumulator drained
@@ -146,70 +151,89 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         }
     } else {
         // ---- epilogue: warps 2..5, each on the tensor-memory lanes of its quarter -----
+        // A thread reads one accumulator row (32 columns at a time); the warp turns the 32 x 32
+        // patch round in shared memory so that each store (and each load of the tensors to add)
+        // covers 32 consecutive columns of one row.
         const int quarter = warp & 3;
+        // per warp: a 32 x 32 patch of 32-bit values (4 KB, 1024-byte aligned for the swizzled
+        // TMA reduction; read back with a 33-float pitch view for the plain store) and the tile's bias
+        unsigned char* epi = smem + STAGES * STAGE + 1024;               // barriers live in the first 1024 bytes
+        float* patch = (float*)(epi + (warp - 2) * 5120);                // 5 KB apart: every patch starts on a 1024-byte boundary
+        float* bias_s = (float*)(epi + 4 * 5120) + (warp - 2) * BN;
+        const unsigned patch_u32 = gl_smem_u32(patch);
         int local = 0;
         TO* O = (TO*)g.out;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+            // before the accumulator is ready: this tile's bias into shared memory
+            for (int j = lane; j < BN; j += 32) bias_s[j] = (g.bias && n0 + j < g.N) ? g.bias[n0 + j] : 0.f;
             bool ok = mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { failed = 1; break; }
             tc_fence_after();
-            const int m = m0 + quarter * 32 + lane;
+            const int mrow0 = m0 + quarter * 32;
             const unsigned trow = tmem_base + buf * BN + ((unsigned)(quarter * 32) << 16);
+            // out_mode 1: tile store by TMA; 2: add-reduction by TMA; 0: element-wise (any alignment,
+            // tensors to add that are not the output)
+            constexpr int CW = sizeof(TO) == 4 ? 32 : 64;              // columns per 128-byte patch row
+            if (out_mode != 0) {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                unsigned r[32];
-                tmem_ld32(trow + c, r);
-                if (m < g.M) {
-                    const int nb = n0 + c;
-                    const size_t o = (size_t)m * g.N + nb;
-                    const bool full = nb + 32 <= g.N && (g.N & 7) == 0;
-                    float v[32];
+                for (int c = 0; c < BN; c += CW) {
+                    unsigned r[32], r2[32];
+                    tmem_ld32(trow + c, r);
+                    if (CW == 64) tmem_ld32(trow + c + 32, r2);
+                    if (lane == 0) bulk_wait_read<0>();                  // the patch's last copy has been read
+                    __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        v[j] = __uint_as_float(r[j]);
-                        if (g.bias && nb + j < g.N) v[j] += g.bias[nb + j];
-                        v[j] = gl_activate<false>(v[j], g.act);
-                    }
-                    if (full) {
-                        if (g.add0) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 t = *(const float4*)(g.add0 + o + j);
-                                v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
-                            }
-                        }
-                        if (g.add1) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 t = *(const float4*)(g.add1 + o + j);
-                                v[j] += t.x; v[j + 1] += t.y; v[j + 2] += t.z; v[j + 3] += t.w;
-                            }
-                        }
-                        if constexpr (sizeof(TO) == 4) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *(float4*)((float*)O + o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    for (int q = 0; q < 8; ++q) {                        // 16-byte chunks, swizzled as TMA expects
+                        uint4 pk;
+                        if (CW == 32) {
+                            pk.x = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 0]) + bias_s[c + 4 * q + 0], g.act));
+                            pk.y = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 1]) + bias_s[c + 4 * q + 1], g.act));
+                            pk.z = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 2]) + bias_s[c + 4 * q + 2], g.act));
+                            pk.w = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 3]) + bias_s[c + 4 * q + 3], g.act));
                         } else {
+                            float v[8];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 pk;
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                pk.x = *(unsigned*)&p0; pk.y = *(unsigned*)&p1; pk.z = *(unsigned*)&p2; pk.w = *(unsigned*)&p3;
-                                *(uint4*)((__nv_bfloat16*)O + o + j) = pk;
+                            for (int e = 0; e < 8; ++e) {
+                                const unsigned raw = q < 4 ? r[8 * q + e] : r2[8 * (q - 4) + e];
+                                v[e] = gl_activate_bf16_grade(__uint_as_float(raw) + bias_s[c + 8 * q + e], g.act);
                             }
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+                            pk.x = *(unsigned*)&p0; pk.y = *(unsigned*)&p1; pk.z = *(unsigned*)&p2; pk.w = *(unsigned*)&p3;
                         }
-                    } else {
-                        for (int j = 0; j < 32 && nb + j < g.N; ++j) {
-                            float y = v[j];
-                            if (g.add0) y += g.add0[o + j];
-                            if (g.add1) y += g.add1[o + j];
-                            gl_store(O + o + j, y);
+                        *(uint4*)((unsigned char*)patch + lane * 128 + ((q ^ (lane & 7)) << 4)) = pk;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && mrow0 < g.M && n0 + c < g.N) {
+                        if (out_mode == 2) tma_reduce_add_2d(&map_out, n0 + c, mrow0, patch_u32);
+                        else tma_store_2d(&map_out, n0 + c, mrow0, patch_u32);
+                        bulk_commit();
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    unsigned r[32];
+                    tmem_ld32(trow + c, r);
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = __uint_as_float(r[j]);
+                    __syncwarp();
+                    const int n = n0 + c + lane;
+                    if (n < g.N) {
+                        const float bv = bias_s[c + lane];
+                        const int rows_here = min(32, g.M - mrow0);
+#pragma unroll 4
+                        for (int rr = 0; rr < rows_here; ++rr) {
+                            float v = gl_activate<false>(patch[rr * 33 + lane] + bv, g.act);
+                            const size_t o = (size_t)(mrow0 + rr) * g.N + n;
+                            if (g.add0) v += g.add0[o];
+                            if (g.add1) v += g.add1[o];
+                            gl_store(O + o, v);
                         }
                     }
                 }
@@ -218,6 +242,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
         }
+        if (lane == 0) bulk_wait<0>();           // every reduction of this thread has reached memory
     }
     tc_fence_before();
     __syncthreads();
@@ -230,7 +255,8 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
 
 template <int BN, int STAGES>
 static constexpr size_t tg_smem() {
-    return (size_t)STAGES * (TG_BM * 128 + BN * 128) + 8 * (2 * STAGES + 4) + 1024;
+    // stages, 1024 bytes of barriers, the epilogue warps' patches and bias rows, room to align the start
+    return (size_t)STAGES * (TG_BM * 128 + BN * 128) + 1024 + 4 * 5120 + 4 * BN * 4 + 1024;
 }
 
 template <int BN, int STAGES, typename TO>
@@ -255,17 +281,36 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     if (rc != GL_OK) return rc;
     rc = gl_cached_map_bf16(&map_w, g.w, (uint64_t)g.N, (uint64_t)g.K, BN, TG_BK);
     if (rc != GL_OK) return rc;
+    // How results leave: by TMA when the output's rows are whole 16-byte units and nothing has to be
+    // loaded: a plain store when nothing is added, an add-reduction for out = out + product (add0
+    // is the output itself, 32-bit); otherwise element by element.
+    int out_mode = 0;
+    CUtensorMap map_out = map_a;
+    GemmArgs ga = g;
+    const bool aligned = (g.N * sizeof(TO)) % 16 == 0 && ((uintptr_t)g.out & 15) == 0;
+    if (aligned && !g.add0 && !g.add1) {
+        out_mode = 1;
+    } else if (aligned && sizeof(TO) == 4 && g.add0 == (const float*)g.out && !g.add1) {
+        out_mode = 2;
+        ga.add0 = nullptr;
+    }
+    if (out_mode != 0) {
+        rc = gl_cached_map(&map_out, g.out, (uint64_t)g.M, (uint64_t)g.N, 32, sizeof(TO) == 4 ? 32 : 64, (uint32_t)sizeof(TO));
+        if (rc != GL_OK) return rc;
+    }
     const int tiles = ((g.M + TG_BM - 1) / TG_BM) * ((g.N + BN - 1) / BN);
     const int grid = tiles < sms ? tiles : sms;
-    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, TG_THREADS, smem, stream>>>(g, map_a, map_w);
+    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_out, out_mode);
     return gl_check_launch();
 }
 
 template <typename TO>
 static int dispatch_bn(const GemmArgs& g, int bn, cudaStream_t stream) {
     if (bn == 256) return launch_tg<256, 4, TO>(g, stream);
+    if (bn == 192) return launch_tg<192, 5, TO>(g, stream);
     if (bn == 128) return launch_tg<128, 6, TO>(g, stream);
     if (bn == 64) return launch_tg<64, 8, TO>(g, stream);
+    if (bn == 160 && sizeof(TO) == 4) return launch_tg<160, 5, TO>(g, stream);    // 160 is no multiple of 64: 32-bit outputs only
     return GL_ERR_SHAPE;
 }
 
@@ -282,17 +327,24 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
     if (g.K <= 0 || g.K % 8) return GL_ERR_SHAPE;
     if (((uintptr_t)g.a | (uintptr_t)g.w) & 15) return GL_ERR_ALIGN;
     if (bn == 0) {
-        // the widest tile whose last wave is not mostly idle
-        int sms = 148;
+        // A tile's time goes with the operand bytes it pulls from L2, about (128 + width); the
+        // grid runs in waves of one tile per SM, and the last wave counts whole.
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
         const int tm = (g.M + TG_BM - 1) / TG_BM;
-        double best = 1e30;
-        const int cands[3] = {256, 128, 64};
-        for (int i = 0; i < 3; ++i) {
+        long best = -1;
+        const int cands[5] = {256, 192, 160, 128, 64};
+        for (int i = 0; i < 5; ++i) {
             const int c = cands[i];
+            if (c == 160 && out_dtype != GL_F32) continue;
             const int tiles = tm * ((g.N + c - 1) / c);
-            const int waves = (tiles + sms - 1) / sms;
-            const double cost = (double)waves * c * (c == 256 ? 1.0 : c == 128 ? 1.3 : 2.0);
-            if (cost < best) { best = cost; bn = c; }
+            const long cost = (long)((tiles + sms - 1) / sms) * (TG_BM + c);
+            if (best < 0 || cost < best) { best = cost; bn = c; }
         }
     }
     if (out_dtype == GL_F32) return dispatch_bn<float>(g, bn, stream);

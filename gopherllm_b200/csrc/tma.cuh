@@ -36,18 +36,20 @@ static gl_encode_tiled_fn gl_get_encode() {
     return fn;
 }
 
-// A box of box_rows x box_cols elements (box_cols * 2 bytes must be 128 for the 128-byte
-// swizzle) over a row-major bf16 matrix; elements outside the matrix read as zero.
-static int gl_make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                            uint32_t box_rows, uint32_t box_cols) {
+// A box of box_rows x box_cols elements (box_cols * elem_bytes must be 128 for the 128-byte
+// swizzle) over a row-major matrix of bf16 (elem_bytes 2) or f32 (4); elements outside the
+// matrix read as zero and are not written.
+static int gl_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                       uint32_t box_rows, uint32_t box_cols, uint32_t elem_bytes) {
     gl_encode_tiled_fn enc = gl_get_encode();
     if (!enc) return GL_ERR_DRIVER;
-    if (((uintptr_t)base & 15) || (cols * 2) % 16) return GL_ERR_ALIGN;
+    if (((uintptr_t)base & 15) || (cols * elem_bytes) % 16) return GL_ERR_ALIGN;
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
+    cuuint64_t strides[1] = {cols * elem_bytes};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                     const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? GL_OK : GL_ERR_DRIVER;
@@ -55,9 +57,10 @@ static int gl_make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, u
 
 // Tensor maps of long-lived matrices (weights) are encoded once and kept.
 struct GlMapKey {
-    const void* base; uint64_t rows, cols; uint32_t box_rows, box_cols;
+    const void* base; uint64_t rows, cols; uint32_t box_rows, box_cols, elem_bytes;
     bool operator==(const GlMapKey& o) const {
-        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols;
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+               elem_bytes == o.elem_bytes;
     }
 };
 struct GlMapKeyHash {
@@ -65,26 +68,30 @@ struct GlMapKeyHash {
         size_t h = (size_t)k.base;
         h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
         h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
-        h ^= ((size_t)k.box_rows << 32 | k.box_cols) + (h << 6) + (h >> 2);
+        h ^= ((size_t)k.box_rows << 32 | k.box_cols) + k.elem_bytes + (h << 6) + (h >> 2);
         return h;
     }
 };
-static int gl_cached_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
-                              uint32_t box_rows, uint32_t box_cols) {
+static int gl_cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                         uint32_t box_rows, uint32_t box_cols, uint32_t elem_bytes) {
     static std::unordered_map<GlMapKey, CUtensorMap, GlMapKeyHash> cache;
     static std::mutex mu;
-    GlMapKey key{base, rows, cols, box_rows, box_cols};
+    GlMapKey key{base, rows, cols, box_rows, box_cols, elem_bytes};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it == cache.end()) {
         CUtensorMap m;
-        int rc = gl_make_map_bf16(&m, base, rows, cols, box_rows, box_cols);
+        int rc = gl_make_map(&m, base, rows, cols, box_rows, box_cols, elem_bytes);
         if (rc != GL_OK) return rc;
         if (cache.size() > 4096) cache.clear();
         it = cache.emplace(key, m).first;
     }
     memcpy(out, &it->second, sizeof(CUtensorMap));
     return GL_OK;
+}
+static int gl_cached_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                              uint32_t box_rows, uint32_t box_cols) {
+    return gl_cached_map(out, base, rows, cols, box_rows, box_cols, 2);
 }
 
 // ---------------------------------------------------------------------------
@@ -129,6 +136,24 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// Tile in shared memory added onto a tile of a 32-bit tensor in global memory (elements
+// outside the tensor are skipped); completion is tracked by the thread's bulk-copy groups.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, unsigned src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+// Tile in shared memory written to a tile of a tensor in global memory (elements outside the
+// tensor are skipped).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, unsigned src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until the shared-memory sources of all but the newest n groups have been read
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

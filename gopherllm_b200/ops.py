@@ -424,7 +424,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
                  add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
-                 tile_n: int = 0) -> torch.Tensor:
+                 tile_n: int = 0, _defines=()) -> torch.Tensor:
     """The tensor-core product (tcgen05.mma fed by TMA, accumulators in tensor memory) for
     bfloat16 operands with K a multiple of 8; meant for many rows."""
     _need(a, "a", torch.bfloat16)
@@ -434,9 +434,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[1] % 8:
         raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
-    if tile_n not in (0, 64, 128, 256):
-        raise KernelError("tile_n is 0 (choose), 64, 128 or 256")
-    fn = _lib("gemm_tcgen05.cu").gl_gemm_tcgen05
+    if tile_n not in (0, 64, 128, 160, 192, 256):
+        raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256")
+    fn = _lib("gemm_tcgen05.cu", _defines).gl_gemm_tcgen05
     _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(tile_n), _stream()), "gemm_tcgen05")
     return out
 

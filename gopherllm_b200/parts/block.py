@@ -42,22 +42,23 @@ class _AssembledBlock(Block):
 
 
 class ParallelBlock(_AssembledBlock):
-    """x ← x + ffn(n) + mixer(n), n = norm(x): one norm feeds both branches
+    """x ← (x + ffn(n)) + mixer(n), n = norm(x): one norm feeds both branches
     (model.go:2738-2740) and both are added to the residual, the feed-forward
     first (model.go:2812-2815)."""
 
     def forward(self, x, ctx, cache):
         xn = self.norm.forward(x, ctx.act_dtype)
-        a = torch.empty_like(x)
         side = getattr(ctx, "side_stream", None)
         if side is None or not hasattr(self.ffn, "begin"):
-            self.mixer.forward(xn, ctx, cache, (), a)
-            self.ffn.forward(xn, ctx, (x, a), x)
+            # each branch adds itself onto the residual stream in its last product's epilogue,
+            # the feed-forward first: (x + mlp) + attn, the reference's order
+            self.ffn.forward(xn, ctx, (x,), x)
+            self.mixer.forward(xn, ctx, cache, (x,), x)
             return x
         # Both branches read the same normalised input, so the feed-forward's first half runs
         # on a second stream beside the mixer: with few tokens every kernel is a stream of
         # weights, and the second stream keeps memory busy while the mixer's small kernels
-        # start and finish.  The branches meet before the second half, which adds them up.
+        # start and finish.  The branches meet before the feed-forward's second half.
         main = torch.cuda.current_stream()
         h = torch.empty(self.ffn.hidden_shape(x.shape[0]), dtype=ctx.act_dtype, device=x.device)
         fork, join = torch.cuda.Event(), torch.cuda.Event()
@@ -66,9 +67,9 @@ class ParallelBlock(_AssembledBlock):
         with torch.cuda.stream(side):
             self.ffn.begin(xn, ctx, out=h)
             join.record(side)
-        self.mixer.forward(xn, ctx, cache, (), a)
+        self.mixer.forward(xn, ctx, cache, (x,), x)
         main.wait_event(join)
-        self.ffn.finish(h, ctx, (x, a), x)
+        self.ffn.finish(h, ctx, (x,), x)
         return x
 
 

@@ -86,18 +86,31 @@ def test_gemm_tcgen05(M, N, K):
     a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
     bias, add0, add1 = rnd(N, seed=2), rnd(M, N, seed=3), rnd(M, N, seed=4)
     ref = ref_linear(a, w, bias, "gelu_new", add0, add1)
-    for tile in (0, 64, 128, 256):
+    for tile in (0, 64, 128, 160, 192, 256):
         got = o.gemm_tcgen05(a, w, bias, "gelu_new", add0, add1, out_dtype=torch.float32, tile_n=tile)
         torch.cuda.synchronize()
         assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
         err = (got.double() - ref).abs().max().item()
         assert err <= 3e-5 * max(1.0, ref.abs().max().item()), (tile, err)
-    got = o.gemm_tcgen05(a, w, bias, None, out_dtype=torch.bfloat16)
+    for act in (None, "gelu_new"):
+        for tile in (0, 64, 192):
+            got = o.gemm_tcgen05(a, w, bias, act, out_dtype=torch.bfloat16, tile_n=tile)
+            ref = ref_linear(a, w, bias, act, None, None)
+            assert (got.double() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item()), (act, tile)
+    for tile in (0, 160, 256):
+        got = o.gemm_tcgen05(a, w, bias, "gelu", out_dtype=torch.float32, tile_n=tile)    # the plain TMA store
+        ref = ref_linear(a, w, bias, "gelu", None, None)
+        assert (got.double() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max().item()), tile
     ref = ref_linear(a, w, bias, None, None, None)
-    assert (got.double() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item())
     x = add0.clone()                                                   # in place on the residual stream
     o.gemm_tcgen05(a, w, bias, None, x, add1, out=x)
     assert (x.double() - ref_linear(a, w, bias, None, add0, add1)).abs().max() <= 3e-5 * max(1.0, ref.abs().max().item())
+    x = add0.clone()                                                   # out = out + product: the add-reduction path
+    o.gemm_tcgen05(a, w, bias, "relu", x, out=x)
+    torch.cuda.synchronize()
+    assert o.wait_failures()["gemm_tcgen05.cu"] == 0
+    want = ref_linear(a, w, bias, "relu", add0, None)
+    assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
 
 
 def test_gemm_tcgen05_one_weight_stands_out():
@@ -108,7 +121,7 @@ def test_gemm_tcgen05_one_weight_stands_out():
     for (n, k) in [(0, 0), (519, 1095), (77, 1029), (256, 63), (255, 64), (128, 15), (127, 16), (511, 1088)]:
         w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
         w[n, k] = 3.0
-        for tile in (64, 128, 256):
+        for tile in (64, 128, 160, 192, 256):
             got = o.gemm_tcgen05(a, w, out_dtype=torch.float32, tile_n=tile)
             want = torch.zeros(M, N, device=DEV)
             want[:, n] = 3.0
