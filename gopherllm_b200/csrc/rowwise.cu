@@ -117,9 +117,83 @@ __global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__
     }
 }
 
+// One warp per row, for many rows: the row lives in registers as NV4 float4 per lane, the
+// statistics need warp shuffles only, loads and stores are 16 bytes (D a multiple of 4).
+template <typename TO, int NV4>
+__global__ void __launch_bounds__(256)
+norm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gamma,
+                 const float* __restrict__ beta, TO* __restrict__ out, int R, int D, float eps, int rms) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= R) return;
+    const float4* xr = (const float4*)(x + (size_t)(rows ? rows[r] : r) * D);
+    const int n4 = D >> 2;
+    float4 v[NV4];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV4; ++i) {
+        const int k = lane + 32 * i;
+        v[i] = k < n4 ? xr[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = rms ? 0.f : gl_warp_sum(s) / (float)D;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV4; ++i) {
+        if (lane + 32 * i < n4) {
+            const float a = v[i].x - mean, b = v[i].y - mean, c = v[i].z - mean, d = v[i].w - mean;
+            q += (a * a + b * b) + (c * c + d * d);
+        }
+    }
+    const float var = gl_warp_sum(q) / (float)D;
+    float inv = 0.f;
+    if (lane == 0) inv = (float)(1.0 / sqrt((double)(var + eps)));
+    inv = __shfl_sync(0xffffffffu, inv, 0);
+    const float4* g4 = (const float4*)gamma;
+    const float4* b4 = (const float4*)beta;
+#pragma unroll
+    for (int i = 0; i < NV4; ++i) {
+        const int k = lane + 32 * i;
+        if (k < n4) {
+            const float4 g = g4[k];
+            float4 y;
+            y.x = (v[i].x - mean) * inv * g.x; y.y = (v[i].y - mean) * inv * g.y;
+            y.z = (v[i].z - mean) * inv * g.z; y.w = (v[i].w - mean) * inv * g.w;
+            if (beta) { const float4 b = b4[k]; y.x += b.x; y.y += b.y; y.z += b.z; y.w += b.w; }
+            if constexpr (sizeof(TO) == 4) {
+                ((float4*)(out + (size_t)r * D))[k] = y;
+            } else {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
+                uint2 pk;
+                pk.x = *(unsigned*)&p0; pk.y = *(unsigned*)&p1;
+                ((uint2*)(out + (size_t)r * D))[k] = pk;
+            }
+        }
+    }
+}
+
+template <typename TO, int NV4>
+static int launch_norm_warp(const float* x, const int* rows, const float* gamma, const float* beta, TO* out,
+                            int R, int D, float eps, int rms, cudaStream_t stream) {
+    return gl_launch(norm_warp_kernel<TO, NV4>, dim3((R + 7) / 8), dim3(256), 0, stream, 1, x, rows, gamma, beta, out, R, D, eps, rms);
+}
+
 template <typename TO>
 static int launch_norm(const float* x, const int* rows, const float* gamma, const float* beta, TO* out,
                        int R, int D, float eps, int rms, cudaStream_t stream) {
+    const bool vec = D % 4 == 0 && !(((uintptr_t)x | (uintptr_t)out | (uintptr_t)gamma | (uintptr_t)beta) & 15);
+    // (the 32-bit path keeps one kernel for every row count, so that a row's result never depends
+    // on how many rows come with it)
+    if (sizeof(TO) == 2 && R >= 256 && vec && D <= 4096) {
+        const int n = (D / 4 + 31) / 32;
+        if (n <= 4) return launch_norm_warp<TO, 4>(x, rows, gamma, beta, out, R, D, eps, rms, stream);
+        if (n <= 8) return launch_norm_warp<TO, 8>(x, rows, gamma, beta, out, R, D, eps, rms, stream);
+        if (n <= 16) return launch_norm_warp<TO, 16>(x, rows, gamma, beta, out, R, D, eps, rms, stream);
+        if (n <= 24) return launch_norm_warp<TO, 24>(x, rows, gamma, beta, out, R, D, eps, rms, stream);
+        return launch_norm_warp<TO, 32>(x, rows, gamma, beta, out, R, D, eps, rms, stream);
+    }
     const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
     const int per = (D + threads - 1) / threads;
     if (per <= 2) return gl_launch(norm_kernel<TO, 2>, dim3(R), dim3(threads), 0, stream, 1, x, rows, gamma, beta, out, D, eps, rms);
