@@ -97,6 +97,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="leave out prefill, batch 1 and batch 64")
+    ap.add_argument("--sections", default="decode,e2e,prefill,points",
+                    help="which measurements to run (for profiling a part): decode,e2e,prefill,points")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -109,6 +111,9 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    sections = set(args.sections.split(","))
+    if args.skip_points:
+        sections -= {"prefill", "points"}
 
     import numpy as np
     import torch
@@ -121,7 +126,7 @@ def main():
     layers_full = cfg["num_hidden_layers"]
     layers = args.layers or layers_full
     K, W, B, C = args.steps, args.warmup, args.batch, args.context
-    max_b = B if args.skip_points else max(B, 64)
+    max_b = max(B, 64) if "points" in sections else B
     model = gl.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max_b * C, layers=layers)
     eng = model.engine
     spec = model.spec
@@ -156,31 +161,35 @@ def main():
             eng.close(s)
         return batch * steps / (ms / 1e3), ms / steps, ctx_mid
 
-    clocks = ClockSampler()
-    clocks.start()
-    value, ms_step, ctx_mid = decode_rate(B, K, W, C)
-    clock_info = clocks.stop()
-    launches_per_step = eng.launches_per_loop_step.get(B, 0)
+    value, ms_step, ctx_mid, clock_info, launches_per_step = 0.0, float("nan"), C - 1 - K / 2.0, {}, 0
+    if "decode" in sections:
+        clocks = ClockSampler()
+        clocks.start()
+        value, ms_step, ctx_mid = decode_rate(B, K, W, C)
+        clock_info = clocks.stop()
+        launches_per_step = eng.launches_per_loop_step.get(B, 0)
 
     # the same work through the Python entry point: host tokens in, host tokens out
-    prompt_len = C - K - W - 1
-    prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(B)]
-    model.generate(prompts[:B], max_tokens=4, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
-                   stop_tokens=(), seed=5)                 # warm-up: captures the decode step for this batch
-    res = model.generate(prompts, max_tokens=K + W, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
-                         stop_tokens=(), seed=5)
-    dec_s = max(r.stats.decode_time for r in res)
-    e2e_value = sum(r.stats.generated_tokens - 1 for r in res) / dec_s
-    e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.h2d_bytes_last + 4 * 0,
-           "d2h_bytes_per_step": 4 * B}
+    e2e = None
+    if "e2e" in sections:
+        prompt_len = C - K - W - 1
+        prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(B)]
+        model.generate(prompts[:B], max_tokens=4, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                       stop_tokens=(), seed=5)             # warm-up: captures the decode step for this batch
+        res = model.generate(prompts, max_tokens=K + W, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                             stop_tokens=(), seed=5)
+        dec_s = max(r.stats.decode_time for r in res)
+        e2e_value = sum(r.stats.generated_tokens - 1 for r in res) / dec_s
+        e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.h2d_bytes_last + 4 * B,
+               "d2h_bytes_per_step": 4 * B}
 
     step_bytes = weight_bytes + B * ctx_mid * kv_per_pos
-    achieved = step_bytes / (ms_step / 1e3) / 1e9
+    achieved = step_bytes / (ms_step / 1e3) / 1e9 if "decode" in sections else 0.0
     out = {
         "metric": "decode tok/s at batch 8, context 2048 (Phi-2 sizes, bf16)" if (B, C) == (8, 2048)
                   else f"decode tok/s at batch {B}, context {C} (Phi-2 sizes, bf16)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms_step, 4) if "decode" in sections else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, token ids uniform in [0,51200)",
         "config": {"model": "Phi-2 sizes (PhiForCausalLM)", "layers": layers, "layers_of_model": layers_full,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
@@ -194,7 +203,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
     }
-    if not args.skip_points:
+    if "prefill" in sections:
         T = 2048
         toks = [int(t) for t in rng.integers(0, V, size=T)]
         s = eng.open()
@@ -217,6 +226,7 @@ def main():
         flops = 2.0 * T * layer_params + 2.0 * T * T * cfg["hidden_size"] * layers + 2.0 * V * cfg["hidden_size"]
         out["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
                           "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    if "points" in sections:
         b1, _, _ = decode_rate(1, min(K, 64), W, C)
         b64, _, _ = decode_rate(64, min(K, 32), W, C)
         out["points"] = {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)}
