@@ -22,7 +22,9 @@ struct SampleArgs {
     int* recent_n;            // [*] how many of them are valid
     unsigned long long* rng;  // [*] generator state, advanced by one draw when a draw is made
     int* out;                 // [B] chosen token
-    int B, V;
+    float* sort_key;          // [B, vpad] scratch for the whole-row nucleus, or null
+    int* sort_idx;            // [B, vpad]
+    int B, V, vpad;           // vpad: a power of two >= V
     int top_k;                // <= 0: all tokens
     float temperature, top_p, min_p, repeat_penalty;
 };
@@ -307,6 +309,123 @@ sample_kernel(SampleArgs a) {
         if (tid == 0) finish(a, b, row, imax);
         return;
     }
+    if (a.top_p < 1.0f || a.min_p > 0.f) {
+        // 5. nucleus over the whole row (sampleTopPFromWeights, sampling.go:171-228): candidates are
+        //    the weights >= 1e-5 of the largest (all of them if that set holds less than top_p of the
+        //    mass), sorted by weight descending then index ascending; min-p and top-p cut the sorted
+        //    list; one draw over what is kept.
+        float* ck = a.sort_key + (size_t)b * a.vpad;
+        int* ci = a.sort_idx + (size_t)b * a.vpad;
+        float mxp = 0.f;
+        for (int i = tid; i < V; i += SM_THREADS) mxp = fmaxf(mxp, w[i]);
+        int dummy;
+        block_argmax(mxp, tid, s_f, s_i, &s_best, &dummy);
+        const float thr = s_best * 1e-5f;
+        if (tid == 0) { s_ngt = 0; }
+        __syncthreads();
+        float kpart = 0.f;
+        for (int i = tid; i < V; i += SM_THREADS) {
+            const float p = w[i];
+            if (p >= thr) {
+                const unsigned slot = atomicAdd(&s_ngt, 1u);
+                ck[slot] = p; ci[slot] = i;
+                kpart += p;
+            }
+        }
+        float kept_sum;
+        block_scan(kpart, s_f, &kept_sum);
+        __syncthreads();
+        int n_c = (int)s_ngt;
+        if (kept_sum < a.top_p * sum) {                  // too little mass: every token is a candidate
+            for (int i = tid; i < V; i += SM_THREADS) { ck[i] = w[i]; ci[i] = i; }
+            n_c = V;
+        }
+        int np = 1;
+        while (np < n_c) np <<= 1;
+        for (int i = n_c + tid; i < np; i += SM_THREADS) { ck[i] = -1.f; ci[i] = 0x7fffffff; }
+        // bitonic sort in global memory (the row's candidates stay in L2), best first
+        for (int size = 2; size <= np; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                __syncthreads();
+                for (int t = tid; t < np / 2; t += SM_THREADS) {
+                    const int lo_i = 2 * t - (t & (stride - 1)), hi_i = lo_i + stride;
+                    const bool up = (lo_i & size) == 0;
+                    const float v0 = ck[lo_i], v1 = ck[hi_i];
+                    const int i0 = ci[lo_i], i1 = ci[hi_i];
+                    const bool first_better = v0 > v1 || (v0 == v1 && i0 < i1);
+                    if (first_better != up) { ck[lo_i] = v1; ck[hi_i] = v0; ci[lo_i] = i1; ci[hi_i] = i0; }
+                }
+            }
+        }
+        __syncthreads();
+        // min-p: the list ends before the first weight below min_p * best; its mass is the new total
+        int cutoff = n_c;
+        float total = sum;
+        if (a.min_p > 0.f) {
+            const float mthr = a.min_p * ck[0];
+            if (tid == 0) s_found = n_c;
+            __syncthreads();
+            for (int i = tid; i < n_c; i += SM_THREADS)
+                if (i > 0 && ck[i] < mthr) atomicMin(&s_found, i);
+            __syncthreads();
+            cutoff = s_found;
+            float mpart = 0.f;
+            for (int i = tid; i < cutoff; i += SM_THREADS) mpart += ck[i];
+            block_scan(mpart, s_f, &total);
+            __syncthreads();
+        }
+        // top-p: the shortest prefix whose mass exceeds top_p * total
+        const float target = a.top_p * total;
+        if (tid == 0) { s_found = 0x7fffffff; s_besti = 0; }
+        __syncthreads();
+        float carry = 0.f, kept = 0.f;
+        for (int base = 0; base < cutoff; base += SM_THREADS) {
+            const int i = base + tid;
+            const float p = i < cutoff ? ck[i] : 0.f;
+            float tot;
+            const float incl = block_scan(p, s_f, &tot) + carry;
+            if (i < cutoff && incl > target) { atomicMin(&s_found, i); s_besti = 1; }
+            carry += tot;
+            __syncthreads();
+            if (s_besti) break;
+        }
+        __syncthreads();
+        if (s_found != 0x7fffffff) cutoff = s_found + 1;
+        // the kept mass: the running sum up to the cut
+        {
+            float kp = 0.f;
+            for (int i = tid; i < cutoff; i += SM_THREADS) kp += ck[i];
+            block_scan(kp, s_f, &kept);
+            __syncthreads();
+        }
+        if (!(kept > 0.f) || !finite_bits(kept)) {
+            if (tid == 0) finish(a, b, row, imax);
+            return;
+        }
+        if (tid == 0) {
+            unsigned long long st = a.rng[row];
+            s_best = rng_next(&st) * kept;
+            a.rng[row] = st;
+            s_found = cutoff - 1;
+            s_besti = 0;
+        }
+        __syncthreads();
+        const float rr = s_best;
+        carry = 0.f;
+        for (int base = 0; base < cutoff; base += SM_THREADS) {
+            const int i = base + tid;
+            const float p = i < cutoff ? ck[i] : 0.f;
+            float tot;
+            const float incl = block_scan(p, s_f, &tot) + carry;
+            if (i < cutoff && incl > rr) { atomicMin(&s_found, i); s_besti = 1; }
+            carry += tot;
+            __syncthreads();
+            if (s_besti) break;
+        }
+        __syncthreads();
+        if (tid == 0) finish(a, b, row, ci[s_found]);
+        return;
+    }
     float r = 0.f;
     if (tid == 0) {
         unsigned long long st = a.rng[row];
@@ -341,7 +460,8 @@ GL_API int gl_sample(const SampleArgs* args, cudaStream_t stream) {
     if (!greedy) {
         if (a.top_k > SM_KMAX && a.top_k < a.V) return GL_ERR_SHAPE;
         const bool whole_row = !(a.top_k > 0 && a.top_k < a.V);
-        if (whole_row && (a.top_p < 1.0f || a.min_p > 0.f)) return GL_ERR_SHAPE;
+        if (whole_row && (a.top_p < 1.0f || a.min_p > 0.f) && (!a.sort_key || !a.sort_idx || a.vpad < a.V))
+            return GL_ERR_SHAPE;
     }
     return gl_launch(sample_kernel, dim3(a.B), dim3(SM_THREADS), 0, stream, 1, a);
 }

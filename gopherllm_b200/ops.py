@@ -465,7 +465,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
 class _SampleArgs(Structure):
     _fields_ = [("logits", c_void_p), ("work", c_void_p), ("state_row", c_void_p), ("recent", c_void_p),
                 ("recent_n", c_void_p), ("rng", c_void_p), ("out", c_void_p),
-                ("B", c_int), ("V", c_int), ("top_k", c_int),
+                ("sort_key", c_void_p), ("sort_idx", c_void_p),
+                ("B", c_int), ("V", c_int), ("vpad", c_int), ("top_k", c_int),
                 ("temperature", c_float), ("top_p", c_float), ("min_p", c_float),
                 ("repeat_penalty", c_float)]
 
@@ -477,15 +478,26 @@ def check_sampler(temperature: float, top_k: int, top_p: float, min_p: float, vo
         return
     whole = not (0 < top_k < vocab)
     if not whole and top_k > SAMPLE_KMAX:
-        raise KernelError(f"top_k {top_k} exceeds {SAMPLE_KMAX}")
-    if whole and (top_p < 1.0 or min_p > 0.0):
-        raise KernelError("top_p < 1 or min_p > 0 need 0 < top_k < vocabulary "
-                          f"(top_k up to {SAMPLE_KMAX}); the whole-vocabulary nucleus is not built")
+        raise KernelError(f"top_k {top_k} exceeds {SAMPLE_KMAX} (top_k 0 or >= vocabulary samples the whole row)")
+
+
+def needs_sort_scratch(temperature: float, top_k: int, top_p: float, min_p: float, vocab: int) -> bool:
+    """True when sampling sorts whole rows (a nucleus or min-p cut with top-k off)."""
+    greedy = temperature < 1e-6 or top_k == 1
+    return (not greedy) and not (0 < top_k < vocab) and (top_p < 1.0 or min_p > 0.0)
+
+
+def sort_scratch_size(vocab: int) -> int:
+    n = 1
+    while n < vocab:
+        n <<= 1
+    return n
 
 
 def sample(logits: torch.Tensor, work: torch.Tensor, recent: torch.Tensor, recent_n: torch.Tensor,
            rng: torch.Tensor, out: torch.Tensor, temperature: float, top_k: int, top_p: float,
-           min_p: float, repeat_penalty: float, state_row: Optional[torch.Tensor] = None) -> None:
+           min_p: float, repeat_penalty: float, state_row: Optional[torch.Tensor] = None,
+           sort_key: Optional[torch.Tensor] = None, sort_idx: Optional[torch.Tensor] = None) -> None:
     """One token per row of float32 logits [B, V] into ``out`` [B] int32.
 
     recent [R, 64] int32 / recent_n [R] int32: each state row's window of recent tokens
@@ -510,8 +522,19 @@ def sample(logits: torch.Tensor, work: torch.Tensor, recent: torch.Tensor, recen
     elif R < B:
         raise KernelError(f"{R} sampler states for {B} rows")
     check_sampler(temperature, top_k, top_p, min_p, V)
+    vpad = 0
+    if needs_sort_scratch(temperature, top_k, top_p, min_p, V):
+        vpad = sort_scratch_size(V)
+        if sort_key is None:
+            sort_key = torch.empty((B, vpad), dtype=torch.float32, device=logits.device)
+            sort_idx = torch.empty((B, vpad), dtype=torch.int32, device=logits.device)
+        _need(sort_key, "sort_key", torch.float32)
+        _need(sort_idx, "sort_idx", torch.int32)
+        if sort_key.numel() < B * vpad or sort_idx.numel() < B * vpad:
+            raise KernelError("sorting scratch is smaller than the batch needs")
     a = _SampleArgs(logits.data_ptr(), work.data_ptr(), _addr(state_row), recent.data_ptr(),
-                    recent_n.data_ptr(), rng.data_ptr(), out.data_ptr(), B, V, top_k,
+                    recent_n.data_ptr(), rng.data_ptr(), out.data_ptr(), _addr(sort_key), _addr(sort_idx),
+                    B, V, vpad, top_k,
                     temperature, top_p, min_p, repeat_penalty)
     _check(_lib("sampling.cu").gl_sample(byref(a), _stream()), "sample")
 

@@ -98,11 +98,17 @@ class DeviceSampler:
         self.recent_n = recent_n.to(device)
         self.out = torch.zeros(n, dtype=torch.int32, device=device)
         self.work = torch.empty((n, vocab), dtype=torch.float32, device=device)
+        self.sort_key = self.sort_idx = None
+        if ops.needs_sort_scratch(config.temperature, config.top_k, config.top_p, config.min_p, vocab):
+            vpad = ops.sort_scratch_size(vocab)
+            self.sort_key = torch.empty((n, vpad), dtype=torch.float32, device=device)
+            self.sort_idx = torch.empty((n, vpad), dtype=torch.int32, device=device)
 
     def sample(self, logits: torch.Tensor, state_row: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Tokens [B] int32 (a view of an internal buffer) for logits [B, V]."""
         c = self.config
         B = logits.shape[0]
         ops.sample(logits, self.work, self.recent, self.recent_n, self.rng, self.out,
-                   c.temperature, c.top_k, c.top_p, c.min_p, c.repeat_penalty, state_row=state_row)
+                   c.temperature, c.top_k, c.top_p, c.min_p, c.repeat_penalty, state_row=state_row,
+                   sort_key=self.sort_key, sort_idx=self.sort_idx)
         return self.out[:B]

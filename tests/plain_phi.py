@@ -296,7 +296,41 @@ def sample(logits, temperature, top_k, top_p, min_p, repeat_penalty, rng, recent
     if not (total > 0) or not np.isfinite(total):
         return int(np.argmax(w))
     if top_p < 1 or min_p > 0:
-        raise NotImplementedError("whole-vocabulary nucleus: not needed by these tests")
+        # sampleTopPFromWeights (sampling.go:171-228)
+        thr = np.float32(w.max() * np.float32(1e-5))
+        cand = [(i, x) for i, x in enumerate(w) if x >= thr]
+        kept_sum = np.float32(0)
+        for _, x in cand:
+            kept_sum = np.float32(kept_sum + x)
+        if kept_sum < np.float32(top_p) * total:
+            cand = list(enumerate(w))
+        cand.sort(key=lambda t: (-t[1], t[0]))
+        cutoff = len(cand)
+        if min_p > 0 and cutoff > 0:
+            mthr = np.float32(min_p) * cand[0][1]
+            total = np.float32(0)
+            for i, (_, x) in enumerate(cand):
+                if i > 0 and x < mthr:
+                    cutoff = i
+                    break
+                total = np.float32(total + x)
+        target = np.float32(top_p) * total
+        cs = np.float32(0)
+        for i in range(cutoff):
+            cs = np.float32(cs + cand[i][1])
+            if cs > target:
+                cutoff = i + 1
+                break
+        kept = cs
+        if not (kept > 0) or not np.isfinite(kept):
+            return int(np.argmax(w))
+        r = np.float32(rng.next_f32() * kept)
+        cs = np.float32(0)
+        for i in range(cutoff):
+            cs = np.float32(cs + cand[i][1])
+            if cs > r:
+                return cand[i][0]
+        return cand[cutoff - 1][0]
     r = rng.next_f32()
     cs = np.float32(0)
     for i, x in enumerate(w):

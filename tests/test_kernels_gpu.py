@@ -381,7 +381,12 @@ def test_sampling_matches_plain(V):
              dict(temperature=1.5, top_k=1, top_p=0.9, min_p=0.0, repeat_penalty=1.0),
              dict(temperature=0.8, top_k=33, top_p=1.0, min_p=0.0, repeat_penalty=1.0),
              dict(temperature=0.8, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0),
-             dict(temperature=1.0, top_k=V + 5, top_p=1.0, min_p=0.0, repeat_penalty=1.2)]
+             dict(temperature=1.0, top_k=V + 5, top_p=1.0, min_p=0.0, repeat_penalty=1.2),
+             # the nucleus over the whole row (top-k off): sorted candidates, min-p and top-p cuts
+             dict(temperature=0.7, top_k=0, top_p=0.9, min_p=0.0, repeat_penalty=1.1),
+             dict(temperature=1.3, top_k=0, top_p=0.5, min_p=0.1, repeat_penalty=1.0),
+             dict(temperature=0.4, top_k=0, top_p=1.0, min_p=0.3, repeat_penalty=1.0),
+             dict(temperature=5.0, top_k=V, top_p=0.97, min_p=0.0, repeat_penalty=1.0)]
     for ci, c in enumerate(cases):
         if c["top_k"] > 0 and c["top_k"] >= V and (c["top_p"] < 1 or c["min_p"] > 0):
             continue
@@ -409,7 +414,8 @@ def test_sampling_matches_plain(V):
                 want = plain_phi.sample(logits[i], c["temperature"], c["top_k"], c["top_p"], c["min_p"],
                                         c["repeat_penalty"], r, rec)
                 whole_row = c["temperature"] >= 1e-6 and not (0 < c["top_k"] < V)
-                if whole_row and got[d][i] != want:
+                nucleus = whole_row and (c["top_p"] < 1 or c["min_p"] > 0)
+                if whole_row and not nucleus and got[d][i] != want:
                     # The whole-row draw walks a running 32-bit sum of V weights; the plain loop adds
                     # them one by one, the kernel by a parallel scan.  Two such sums of n terms with
                     # total 1 differ by at most n * 2^-24, so the draw u may fall on either side of a
