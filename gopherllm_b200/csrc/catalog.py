@@ -8,7 +8,9 @@ GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu",
            "sampling.cu")
 
 # libraries compiled once per head size (GL_HEAD_DIM)
-PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu")
+PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu")
+# libraries that take only some head sizes
+MAX_HEAD_DIM = {"attention_prefill_tc.cu": 128}
 
 
 def head_dim_defines(head_dim: int) -> Tuple[str, ...]:
@@ -20,4 +22,5 @@ def all_libraries(head_dims: Iterable[int] = ()) -> Iterator[Tuple[str, Tuple[st
         yield src, ()
     for hd in sorted(set(int(h) for h in head_dims)):
         for src in PER_HEAD_DIM:
-            yield src, head_dim_defines(hd)
+            if hd <= MAX_HEAD_DIM.get(src, 1 << 30):
+                yield src, head_dim_defines(hd)

@@ -19,6 +19,7 @@
 // leaves its loops, frees its tensor memory and returns.
 #include "common.cuh"
 #include "tma.cuh"
+#include "tcgen05.cuh"
 
 #define TG_BM 128
 #define TG_BK 64
@@ -34,42 +35,9 @@ struct GemmArgs {
     int M, N, K, act;
 };
 
-// shared-memory matrix descriptor: K-major tile of 128-byte rows, 128-byte swizzle,
-// 8-row groups 1024 bytes apart, descriptor version 1 (sm_100)
-__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);          // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                               // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                               // version
-    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
-    return d;
-}
-// instruction descriptor: bf16 x bf16 -> f32, A and B K-major, M 128, N bn
-__host__ __device__ constexpr uint32_t umma_idesc(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TG_BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, uint64_t da, uint64_t db, uint32_t idesc, unsigned accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
+// K-major operand tile of 128-byte rows (64 bf16 of K), 128-byte swizzle
+__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) { return umma_tile_desc(smem_addr, 128); }
+__host__ __device__ constexpr uint32_t umma_idesc(int bn) { return umma_idesc_bf16(bn, 0); }
 
 template <int BN, int STAGES, typename TO>
 __global__ void __launch_bounds__(TG_THREADS, 1)

@@ -36,52 +36,57 @@ static gl_encode_tiled_fn gl_get_encode() {
     return fn;
 }
 
-// A box of box_rows x box_cols elements (box_cols * elem_bytes must be 128 for the 128-byte
-// swizzle) over a row-major matrix of bf16 (elem_bytes 2) or f32 (4); elements outside the
-// matrix read as zero and are not written.
+// A box of box_rows x box_cols elements over a row-major matrix of bf16 (elem_bytes 2) or f32 (4)
+// whose rows lie pitch_elems apart (0: cols).  The box's row (box_cols * elem_bytes = 128, 64 or 32
+// bytes) is the swizzle span.  Elements outside the matrix read as zero and are not written.
 static int gl_make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                       uint32_t box_rows, uint32_t box_cols, uint32_t elem_bytes) {
+                       uint32_t box_rows, uint32_t box_cols, uint32_t elem_bytes, uint64_t pitch_elems = 0) {
     gl_encode_tiled_fn enc = gl_get_encode();
     if (!enc) return GL_ERR_DRIVER;
-    if (((uintptr_t)base & 15) || (cols * elem_bytes) % 16) return GL_ERR_ALIGN;
+    const uint64_t pitch = pitch_elems ? pitch_elems : cols;       // elements between rows
+    if (((uintptr_t)base & 15) || (pitch * elem_bytes) % 16) return GL_ERR_ALIGN;
+    const uint32_t row_bytes = box_cols * elem_bytes;              // the swizzle span is the box's row
+    const CUtensorMapSwizzle swz = row_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                 : row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE;
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * elem_bytes};
+    cuuint64_t strides[1] = {pitch * elem_bytes};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                      const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? GL_OK : GL_ERR_DRIVER;
 }
 
 // Tensor maps of long-lived matrices (weights) are encoded once and kept.
 struct GlMapKey {
-    const void* base; uint64_t rows, cols; uint32_t box_rows, box_cols, elem_bytes;
+    const void* base; uint64_t rows, cols, pitch; uint32_t box_rows, box_cols, elem_bytes;
     bool operator==(const GlMapKey& o) const {
-        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
-               elem_bytes == o.elem_bytes;
+        return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows &&
+               box_cols == o.box_cols && elem_bytes == o.elem_bytes;
     }
 };
 struct GlMapKeyHash {
     size_t operator()(const GlMapKey& k) const {
         size_t h = (size_t)k.base;
         h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
-        h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+        h ^= (k.cols + 31 * k.pitch) * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
         h ^= ((size_t)k.box_rows << 32 | k.box_cols) + k.elem_bytes + (h << 6) + (h >> 2);
         return h;
     }
 };
 static int gl_cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
-                         uint32_t box_rows, uint32_t box_cols, uint32_t elem_bytes) {
+                         uint32_t box_rows, uint32_t box_cols, uint32_t elem_bytes, uint64_t pitch_elems = 0) {
     static std::unordered_map<GlMapKey, CUtensorMap, GlMapKeyHash> cache;
     static std::mutex mu;
-    GlMapKey key{base, rows, cols, box_rows, box_cols, elem_bytes};
+    GlMapKey key{base, rows, cols, pitch_elems, box_rows, box_cols, elem_bytes};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it == cache.end()) {
         CUtensorMap m;
-        int rc = gl_make_map(&m, base, rows, cols, box_rows, box_cols, elem_bytes);
+        int rc = gl_make_map(&m, base, rows, cols, box_rows, box_cols, elem_bytes, pitch_elems);
         if (rc != GL_OK) return rc;
         if (cache.size() > 4096) cache.clear();
         it = cache.emplace(key, m).first;

@@ -269,6 +269,23 @@ def attention_prefill(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, p
     _check(lib.gl_attention_prefill(byref(a), _stream()), "attention_prefill")
 
 
+def attention_prefill_tc(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+                         num_heads: int, num_kv_heads: int, head_dim: int, max_qlen: int,
+                         window: int = 0) -> None:
+    """Causal attention of runs of new tokens over the bfloat16 cache on the 5th-generation
+    tensor cores (tcgen05.mma for both products, operands by TMA, scores and partial outputs
+    in tensor memory); head sizes 16..128 in steps of 16."""
+    if head_dim % 16 or not 16 <= head_dim <= 128:
+        raise KernelError(f"tcgen05 prefill attention takes head sizes 16..128 in steps of 16, not {head_dim}")
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise KernelError("prefill attention takes bfloat16 queries and cache")
+    a = _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
+                   num_heads, num_kv_heads, head_dim, window, max_qlen, 1.0)
+    lib = _lib("attention_prefill_tc.cu", catalog.head_dim_defines(head_dim))
+    _check(lib.gl_attention_prefill_tc(byref(a), c_int(q.shape[0]), c_int(k_cache.shape[0]), _stream()),
+           "attention_prefill_tc")
+
+
 class _DecodeArgs(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("seq_ctx", c_void_p), ("pages", c_void_p), ("part_o", c_void_p), ("part_ml", c_void_p),
@@ -446,6 +463,9 @@ def wait_failures() -> dict:
     out = {}
     for src, fn in (("gemm_tcgen05.cu", "gl_gemm_tcgen05_wait_failed"), ("gemm_skinny.cu", "gl_gemm_skinny_wait_failed")):
         out[src] = int(getattr(_lib(src), fn)())
+    for key, lib in list(build._loaded.items()):
+        if "attention_prefill_tc" in key:
+            out[key] = int(lib.gl_attention_prefill_tc_wait_failed())
     return out
 
 

@@ -212,6 +212,13 @@ def ref_attention(q, k, v, ctx, qlen, window):
     return out
 
 
+@pytest.mark.parametrize("nH,nKV,hd", [(3, 3, 16), (4, 2, 80), (6, 1, 48), (5, 5, 32), (2, 2, 128), (2, 1, 64), (2, 2, 96), (1, 1, 112)])
+@pytest.mark.parametrize("window", [0, 37, 150])
+def test_attention_prefill_tc(nH, nKV, hd, window):
+    run_attention("prefill_tc", torch.bfloat16, nH, nKV, hd, window, [0, 130, 63, 5, 200], [70, 1, 66, 9, 300])
+    assert all(v == 0 for v in ops().wait_failures().values()), "a bounded wait ran out"
+
+
 @pytest.mark.parametrize("nH,nKV,hd", [(3, 3, 16), (4, 2, 80), (6, 1, 48), (2, 2, 256), (5, 5, 32), (2, 2, 128)])
 @pytest.mark.parametrize("window", [0, 37, 150])
 def test_attention_prefill(nH, nKV, hd, window):
@@ -237,7 +244,7 @@ def run_attention(kernel, dtype, nH, nKV, hd, window, ctxs, qlens):
     out = torch.empty(T, nH * hd, dtype=dtype, device=DEV)
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     starts = np.concatenate([[0], np.cumsum(qlens)[:-1]]).tolist()
-    fn = o.attention_generic if kernel == "generic" else o.attention_prefill
+    fn = {"generic": o.attention_generic, "prefill": o.attention_prefill, "prefill_tc": o.attention_prefill_tc}[kernel]
     fn(q.reshape(T, nH * hd), out, kc, vc, i32(starts), i32(qlens), i32(ctxs), table,
        nH, nKV, hd, max(qlens), window)
     tol = 2e-5 if dtype == torch.float32 else 2 ** -7
@@ -274,7 +281,7 @@ def test_attention_decode(nH, nKV, hd, window):
             assert (got - ref).abs().max() <= 2 ** -7 * max(1.0, ref.abs().max().item()), (b, splits)
 
 
-@pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode", "prefill", "prefill_tc"])
 def test_attention_far_key_and_window_edge(kernel):
     """One key among hundreds carries the whole weight: its value must come back.  With a
     window the key at the window's edge is seen and the one before it is not."""
@@ -297,6 +304,8 @@ def test_attention_far_key_and_window_edge(kernel):
             o.attention_decode(qd, out, kc, vc, i32([L - 1]), table, nH, nKV, hd, 3, window)
         elif kernel == "prefill":
             o.attention_prefill(qd, out, kc, vc, i32([0]), i32([1]), i32([L - 1]), table, nH, nKV, hd, 1, window)
+        elif kernel == "prefill_tc":
+            o.attention_prefill_tc(qd, out, kc, vc, i32([0]), i32([1]), i32([L - 1]), table, nH, nKV, hd, 1, window)
         else:
             o.attention_generic(qd, out, kc, vc, i32([0]), i32([1]), i32([L - 1]), table, nH, nKV, hd, 1, window)
         got = out.reshape(nH, hd).float().cpu()
