@@ -128,6 +128,13 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// the same question without waiting at all
+__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: false (and the failure word set) if the phase never completed.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
     for (unsigned i = 0; i < GL_SPIN_LIMIT; ++i)

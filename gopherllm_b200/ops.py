@@ -372,6 +372,10 @@ def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads
                          head_dim, splits, window)
         return
     if q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0:
+        if USE_TCGEN05 and head_dim <= TC_ATTENTION_MAX_HEAD_DIM:
+            attention_prefill_tc(q, out, k_cache, v_cache, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_ctx, pages,
+                                 num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)
+            return
         attention_prefill(q, out, k_cache, v_cache, ctx.seq_qstart, ctx.seq_qlen, ctx.seq_ctx, pages,
                           num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)
         return
@@ -419,6 +423,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
 
 SKINNY_MAX_ROWS = 64
 USE_TCGEN05 = True
+TC_ATTENTION_MAX_HEAD_DIM = catalog.MAX_HEAD_DIM["attention_prefill_tc.cu"]
 
 
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
