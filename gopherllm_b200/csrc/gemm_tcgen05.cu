@@ -35,6 +35,37 @@ struct GemmArgs {
     int M, N, K, act;
 };
 
+// The work of one block: whole output tiles taken round-robin, or (split) an equal share of all
+// (tile, k-block) units in tile order, which cuts tiles where shares meet.  A cut tile is finished by
+// two or more blocks, each adding its part onto the output, so split work needs the add-reduction
+// epilogue and no activation; the part that starts at k-block 0 carries the bias.
+struct TgWork {
+    long long u, end;
+    int tile, step, n_tiles, k_blocks, split;
+    __device__ TgWork(int n_tiles_, int k_blocks_, int split_) : n_tiles(n_tiles_), k_blocks(k_blocks_), split(split_) {
+        const long long units = (long long)n_tiles * k_blocks;
+        u = units * blockIdx.x / gridDim.x;
+        end = units * (blockIdx.x + 1) / gridDim.x;
+        tile = blockIdx.x;
+        step = gridDim.x;
+    }
+    __device__ bool next(int& t, int& kb0, int& kb1) {
+        if (!split) {
+            if (tile >= n_tiles) return false;
+            t = tile; kb0 = 0; kb1 = k_blocks;
+            tile += step;
+            return true;
+        }
+        if (u >= end) return false;
+        t = (int)(u / k_blocks);
+        kb0 = (int)(u % k_blocks);
+        const long long left = end - u;
+        kb1 = (left < k_blocks - kb0) ? kb0 + (int)left : k_blocks;
+        u += kb1 - kb0;
+        return true;
+    }
+};
+
 // K-major operand tile of 128-byte rows (64 bf16 of K), 128-byte swizzle
 __device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) { return umma_tile_desc(smem_addr, 128); }
 __host__ __device__ constexpr uint32_t umma_idesc(int bn) { return umma_idesc_bf16(bn, 0); }
@@ -42,7 +73,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(int bn) { return umma_idesc_bf
 template <int BN, int STAGES, typename TO>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_out, int out_mode) {
+                    const __grid_constant__ CUtensorMap map_out, int out_mode, int split) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int A_BYTES = TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
     constexpr unsigned TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);   // a power of two holding both accumulators
@@ -79,10 +110,11 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     if (warp == 0) {
         // ---- TMA producer -------------------------------------------------
         if (lane == 0) {
-            int it = 0;
-            for (int tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x) {
+            int it = 0, tile, kb0, kb1;
+            TgWork work(n_tiles, k_blocks, split);
+            while (!failed && work.next(tile, kb0, kb1)) {
                 const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1)) { failed = 1; break; }
                     const unsigned sb = base + s * STAGE;
@@ -96,13 +128,14 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         // ---- MMA issuer ------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BN);
-            int it = 0, local = 0;
-            for (int tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x, ++local) {
+            int it = 0, local = 0, tile, kb0, kb1;
+            TgWork work(n_tiles, k_blocks, split);
+            for (; !failed && work.next(tile, kb0, kb1); ++local) {
                 const int buf = local & 1;
                 if (local >= 2 && !mbar_wait(bar_tempty + 8 * buf, ((local >> 1) - 1) & 1)) { failed = 1; break; }
                 tc_fence_after();
                 const unsigned d = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) { failed = 1; break; }
                     tc_fence_after();
@@ -110,7 +143,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     const uint64_t da = umma_desc(sb), db = umma_desc(sb + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < TG_BK / 16; ++k)     // 32 bytes further along the swizzled row per K 16
-                        umma_bf16(d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                        umma_bf16(d, da + 2 * k, db + 2 * k, idesc, kb != kb0 || k != 0);
                     umma_commit(bar_empty + 8 * s);          // the stage is free once these products have read it
                 }
                 if (failed) break;
@@ -129,13 +162,14 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         float* patch = (float*)(epi + (warp - 2) * 5120);                // 5 KB apart: every patch starts on a 1024-byte boundary
         float* bias_s = (float*)(epi + 4 * 5120) + (warp - 2) * BN;
         const unsigned patch_u32 = gl_smem_u32(patch);
-        int local = 0;
+        int local = 0, tile, kb0, kb1;
         TO* O = (TO*)g.out;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+        TgWork work(n_tiles, k_blocks, split);
+        for (; work.next(tile, kb0, kb1); ++local) {
             const int buf = local & 1;
             const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
             // before the accumulator is ready: this tile's bias into shared memory
-            for (int j = lane; j < BN; j += 32) bias_s[j] = (g.bias && n0 + j < g.N) ? g.bias[n0 + j] : 0.f;
+            for (int j = lane; j < BN; j += 32) bias_s[j] = (g.bias && kb0 == 0 && n0 + j < g.N) ? g.bias[n0 + j] : 0.f;
             bool ok = mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { failed = 1; break; }
@@ -227,6 +261,13 @@ static constexpr size_t tg_smem() {
     return (size_t)STAGES * (TG_BM * 128 + BN * 128) + 1024 + 4 * 5120 + 4 * BN * 4 + 1024;
 }
 
+// 0 (the default) never cuts tiles: inside a model step, where the products run back to back at the
+// power limit, cutting gained nothing measurable, and whole tiles keep the sums in one order.  1 cuts
+// whenever the epilogue allows; -1 cuts when whole tiles would leave more than 8% of the SMs' slots empty
+// (alone and from a cold L2 that took a 2048 x 2560 x 10240 product from 142 to 120 us).
+static int tg_split_mode = 0;
+GL_API void gl_gemm_tcgen05_set_split(int mode) { tg_split_mode = mode; }
+
 template <int BN, int STAGES, typename TO>
 static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     constexpr size_t smem = tg_smem<BN, STAGES>();
@@ -267,8 +308,16 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
         if (rc != GL_OK) return rc;
     }
     const int tiles = ((g.M + TG_BM - 1) / TG_BM) * ((g.N + BN - 1) / BN);
-    const int grid = tiles < sms ? tiles : sms;
-    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_out, out_mode);
+    // Tiles that fill the SMs unevenly are cut where the blocks' equal shares meet, if the epilogue can
+    // add parts onto the output and every share still holds a fair run of k-blocks.
+    const int k_blocks = (g.K + TG_BK - 1) / TG_BK;
+    const int waves = (tiles + sms - 1) / sms;
+    const bool uneven = tiles % sms != 0 && (long long)tiles * 100 < (long long)waves * sms * 92;
+    // (alone it pays only for a long K: a cut tile costs a second add-reduction of its 32-bit patch)
+    const bool can_split = out_mode == 2 && g.act == GL_ACT_NONE && (long long)tiles * k_blocks >= 8LL * sms;
+    const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64));
+    const int grid = split ? sms : (tiles < sms ? tiles : sms);
+    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_out, out_mode, split);
     return gl_check_launch();
 }
 
@@ -311,6 +360,8 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
             const int c = cands[i];
             if (c == 160 && out_dtype != GL_F32) continue;
             const int tiles = tm * ((g.N + c - 1) / c);
+            // (tiles that will be cut into equal shares are not modelled here: the widest tile that
+            // the rule below picks is also the one that cuts best)
             const long cost = (long)((tiles + sms - 1) / sms) * (TG_BM + c);
             if (best < 0 || cost < best) { best = cost; bn = c; }
         }

@@ -426,6 +426,13 @@ USE_TCGEN05 = True
 TC_ATTENTION_MAX_HEAD_DIM = catalog.MAX_HEAD_DIM["attention_prefill_tc.cu"]
 
 
+def gemm_tcgen05_cut_tiles(mode: int) -> None:
+    """How the tcgen05 product shares work when it adds onto its output: 0 whole tiles (default),
+    1 equal shares of (tile, k-block) units whenever possible, -1 shares only when whole tiles would
+    fill the SMs unevenly."""
+    _lib("gemm_tcgen05.cu").gl_gemm_tcgen05_set_split(c_int(mode))
+
+
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
                 add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,

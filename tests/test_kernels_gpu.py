@@ -113,6 +113,41 @@ def test_gemm_tcgen05(M, N, K):
     assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("M,N,K", [(1024, 2560, 1024), (520, 1300, 4104), (2048, 2560, 2560)])
+def test_gemm_tcgen05_cut_tiles(M, N, K):
+    """out = out + product at sizes whose tiles fill the SMs unevenly: the blocks share (tile, k-block)
+    units equally and tiles cut between blocks are summed by the add-reduction; the bias counts once."""
+    o = ops()
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    bias, x0 = rnd(N, seed=2), rnd(M, N, seed=3)
+    want = ref_linear(a, w, bias, None, x0, None)
+    o.gemm_tcgen05_cut_tiles(1)
+    try:
+        _cut_tiles_checks(o, a, w, bias, x0, want, M, N, K)
+    finally:
+        o.gemm_tcgen05_cut_tiles(0)
+
+
+def _cut_tiles_checks(o, a, w, bias, x0, want, M, N, K):
+    for tile in (0, 128, 256):
+        x = x0.clone()
+        o.gemm_tcgen05(a, w, bias, None, x, out=x, tile_n=tile)
+        torch.cuda.synchronize()
+        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        err = (x.double() - want).abs().max().item()
+        assert err <= 3e-5 * max(1.0, want.abs().max().item()), (tile, err)
+    # one weight far along K reaches one column exactly, whichever block holds its k-block
+    a1 = torch.ones(M, K, dtype=torch.bfloat16, device=DEV)
+    for (n, k) in [(0, 0), (N - 1, K - 1), (N // 2 + 3, K // 2 + 9), (255, 64), (256, 63)]:
+        w1 = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
+        w1[n, k] = 3.0
+        x = torch.zeros(M, N, device=DEV)
+        o.gemm_tcgen05(a1, w1, None, None, x, out=x)
+        expect = torch.zeros(M, N, device=DEV)
+        expect[:, n] = 3.0
+        assert torch.equal(x, expect), (n, k)
+
+
 def test_gemm_tcgen05_one_weight_stands_out():
     """A single large weight must reach exactly one output column, wherever it sits in K and N."""
     o = ops()
