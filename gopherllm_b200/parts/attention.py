@@ -16,6 +16,8 @@ class Attention(Mixer):
     q and k, position encoding, query scale, cache write, attention over the
     cache, output projection.  Grouped-query attention when num_kv_heads <
     num_heads (query head h reads group h / (nH/nKV), model.go:2828)."""
+
+    deferred_add = True
     capturable = True
 
     def __init__(self, spec: MixerSpec):
@@ -84,10 +86,11 @@ class Attention(Mixer):
         o = torch.empty_like(q)
         ops.attention(q, o, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads,
                       s.head_dim, window=s.window)
-        a0 = add[0] if len(add) > 0 else None
-        a1 = add[1] if len(add) > 1 else None
         if len(add) > 2:
             raise ValueError("at most two tensors can be added in the projection's epilogue")
+        add = [a() if callable(a) else a for a in add]
+        a0 = add[0] if len(add) > 0 else None
+        a1 = add[1] if len(add) > 1 else None
         return ops.linear(o, self.w_out, self.b_out, add0=a0, add1=a1, out=out)
 
 

@@ -96,6 +96,11 @@ class Mixer(Part):
     def cache_request(self):
         return None
 
+    # A mixer that sets this accepts callables among ``add``: it calls them just before its last
+    # product and adds what they return.  A block uses that to let another branch run beside the
+    # mixer on a second stream and join only where its result is needed.
+    deferred_add = False
+
     def forward(self, xn, ctx, cache, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 

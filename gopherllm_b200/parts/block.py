@@ -49,27 +49,31 @@ class ParallelBlock(_AssembledBlock):
     def forward(self, x, ctx, cache):
         xn = self.norm.forward(x, ctx.act_dtype)
         side = getattr(ctx, "side_stream", None)
-        if side is None or not hasattr(self.ffn, "begin"):
+        if side is None or not self.mixer.deferred_add:
             # each branch adds itself onto the residual stream in its last product's epilogue,
             # the feed-forward first: (x + mlp) + attn, the reference's order
             self.ffn.forward(xn, ctx, (x,), x)
             self.mixer.forward(xn, ctx, cache, (x,), x)
             return x
-        # Both branches read the same normalised input, so the feed-forward's first half runs
-        # on a second stream beside the mixer: with few tokens every kernel is a stream of
-        # weights, and the second stream keeps memory busy while the mixer's small kernels
-        # start and finish.  The branches meet before the feed-forward's second half.
+        # Both branches read the same normalised input, so the feed-forward runs on a second
+        # stream beside the mixer and leaves its result in a buffer of its own; the mixer's last
+        # product adds both the residual and that buffer.  With few tokens every kernel is a
+        # stream of weights: the second stream keeps memory busy while the mixer's small kernels
+        # start and finish, and nothing of the feed-forward is left on the path from one layer's
+        # norm to the next.  The sum is the same three terms in 32-bit, added as (attn + x) + mlp.
         main = torch.cuda.current_stream()
-        h = torch.empty(self.ffn.hidden_shape(x.shape[0]), dtype=ctx.act_dtype, device=x.device)
+        y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         fork, join = torch.cuda.Event(), torch.cuda.Event()
         fork.record(main)
         side.wait_event(fork)
         with torch.cuda.stream(side):
-            self.ffn.begin(xn, ctx, out=h)
+            self.ffn.forward(xn, ctx, (), y)
             join.record(side)
-        self.mixer.forward(xn, ctx, cache, (x,), x)
-        main.wait_event(join)
-        self.ffn.finish(h, ctx, (x,), x)
+        def mlp():                   # resolved by the mixer just before its last product
+            main.wait_event(join)
+            return y
+
+        self.mixer.forward(xn, ctx, cache, (x, mlp), x)
         return x
 
 

@@ -36,19 +36,9 @@ class DenseFeedForward(FeedForward):
         self.b_up, self.b_down = t.get("up.bias"), t.get("down.bias")
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
-        return self.finish(self.begin(xn, ctx), ctx, add, out)
-
-    # The two halves, for a block that runs the first one beside its mixer: ``begin`` needs
-    # only the normalised input, ``finish`` takes what is added to the result.
-    def begin(self, xn, ctx, out: torch.Tensor = None) -> torch.Tensor:
-        return ops.linear(xn, self.w_up, self.b_up, act=self.spec.activation, out_dtype=ctx.act_dtype, out=out)
-
-    def hidden_shape(self, rows: int):
-        return (rows, self.spec.intermediate)
-
-    def finish(self, h, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         if len(add) > 2:
             raise ValueError("at most two tensors can be added in the projection's epilogue")
+        h = ops.linear(xn, self.w_up, self.b_up, act=self.spec.activation, out_dtype=ctx.act_dtype)
         a0 = add[0] if len(add) > 0 else None
         a1 = add[1] if len(add) > 1 else None
         return ops.linear(h, self.w_down, self.b_down, add0=a0, add1=a1, out=out)
