@@ -254,6 +254,14 @@ def test_attention_prefill_tc(nH, nKV, hd, window):
     assert all(v == 0 for v in ops().wait_failures().values()), "a bounded wait ran out"
 
 
+@pytest.mark.parametrize("hd,window", [(80, 0), (128, 0), (64, 333)])
+def test_attention_prefill_tc_long(hd, window):
+    """Many pages: the key and value rings wrap several times, the two tiles of a block end on
+    different pages, and a sequence's rows start deep in its context."""
+    run_attention("prefill_tc", torch.bfloat16, 2, 1, hd, window, [700, 0, 1111], [1500, 517, 130])
+    assert all(v == 0 for v in ops().wait_failures().values()), "a bounded wait ran out"
+
+
 @pytest.mark.parametrize("nH,nKV,hd", [(3, 3, 16), (4, 2, 80), (6, 1, 48), (2, 2, 256), (5, 5, 32), (2, 2, 128)])
 @pytest.mark.parametrize("window", [0, 37, 150])
 def test_attention_prefill(nH, nKV, hd, window):
