@@ -42,6 +42,10 @@ class PositionSpec:
     rotary_dim: int = 0
     theta: float = 10000.0
     interleaved: bool = False
+    extra: Tuple[Tuple[str, object], ...] = ()   # free-form options for other encodings
+
+    def option(self, key, default=None):
+        return dict(self.extra).get(key, default)
 
 
 @dataclass(frozen=True)

@@ -325,3 +325,176 @@ def test_toy_mixer_with_state_registered_built_and_stepped(dtype):
             m.close_sequence(sl)
     got = m.generate(seqs[1], max_tokens=5, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, stop_tokens=())
     assert len(got.tokens) == 5
+
+
+# --------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, defined here, registered and run
+# without a change to the package: a toy, not anybody's model.
+def define_toy_routed():
+    from gopherllm_b200.config import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec)
+    from gopherllm_b200.config.registry import Architecture, register_architecture, resolve_architecture
+    from gopherllm_b200.config.specs import default_schedule
+    from gopherllm_b200.parts import FeedForward, ParamSpec, PositionEncoding, register_feed_forward, register_position
+
+    class StretchedRope(PositionEncoding):
+        """Rotary angles of position / stretch (tables made with torch, in 64-bit)."""
+        def __init__(self, spec):
+            self.spec, self.stretch = spec, float(spec.option("stretch", 1.0))
+
+        def tables(self, ctx):
+            key = ("stretched", self.spec.rotary_dim, self.spec.theta, self.stretch)
+            if key not in ctx.scratch:
+                half = self.spec.rotary_dim // 2
+                inv = self.spec.theta ** (-torch.arange(half, dtype=torch.float64, device=ctx.device) * 2 / self.spec.rotary_dim)
+                ang = (ctx.tok_pos.double() / self.stretch)[:, None] * inv[None, :]
+                ctx.scratch[key] = (ang.cos().float().contiguous(), ang.sin().float().contiguous())
+            return ctx.scratch[key]
+
+    class TopOneExperts(FeedForward):
+        """Router logits and their softmax in 32-bit; a token goes to its best expert and the result is
+        weighted with that expert's probability."""
+        def __init__(self, spec):
+            self.spec, self.n = spec, int(spec.option("experts", 2))
+
+        def parameters(self):
+            s = self.spec
+            return {"router.weight": ParamSpec((self.n, s.hidden)),
+                    "up.weight": ParamSpec((self.n * s.intermediate, s.hidden)),
+                    "down.weight": ParamSpec((self.n * s.hidden, s.intermediate))}
+
+        def load(self, t):
+            s = self.spec
+            self.router = t["router.weight"]
+            self.up = t["up.weight"].reshape(self.n, s.intermediate, s.hidden)
+            self.down = t["down.weight"].reshape(self.n, s.hidden, s.intermediate)
+
+        def forward(self, xn, ctx, add, out):
+            p = torch.softmax(xn.float() @ self.router.float().T, -1)
+            gate, choice = p.max(-1)
+            res = torch.zeros(xn.shape, dtype=torch.float32, device=xn.device)
+            for e in range(self.n):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(xn[rows].float() @ self.up[e].float().T).to(xn.dtype).float()
+                    res[rows] = gate[rows, None] * (h @ self.down[e].float().T)
+            for a in add:
+                res = res + a
+            out.copy_(res)
+            return out
+
+    if resolve_architecture("toy-routed") is None:
+        register_position("stretched_rope", StretchedRope)
+        register_feed_forward("top_one_experts", TopOneExperts)
+
+        @dataclass
+        class RoutedConfig:
+            hidden_size: int = 40
+            vocab_size: int = 77
+            experts: int = 3
+            stretch: float = 4.0
+            torch_dtype: str = "bfloat16"
+            initializer_range: float = 0.2
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+            def to_dict(self):
+                return dict(architectures=["ToyRoutedForCausalLM"], model_type="toy-routed", **self.__dict__)
+
+        def spec_of(c):
+            norm = NormSpec("layernorm", c.hidden_size, 1e-6, bias=True)
+            pos = PositionSpec("stretched_rope", 8, 50.0, extra=(("stretch", c.stretch),))
+            att = MixerSpec("attention", c.hidden_size, 2, 2, 16, 0, 0.25, True, None, pos)
+            ffn = FeedForwardSpec("top_one_experts", c.hidden_size, 24, "relu", False, extra=(("experts", c.experts),))
+            layers = (BlockSpec("parallel", norm, att, ffn), BlockSpec("sequential", norm, att, ffn, norm))
+            return ModelSpec(c.hidden_size, c.vocab_size, 256, layers, default_schedule(2), norm,
+                             tie_embeddings=False, head_bias=True)
+
+        class Names:
+            embedding, final_norm, head = "emb.weight", "norm_f", "head"
+
+            def __init__(self, c):
+                pass
+
+            def layer(self, i, slot, key):
+                return f"h.{i}.{slot}.{key}"
+
+        register_architecture(Architecture("toy-routed", RoutedConfig, spec_of, Names), aliases=["ToyRouted"])
+    return resolve_architecture("toy-routed")
+
+
+def toy_routed_plain(tokens, W, cfg, act_dtype):
+    """The routed toy written out plainly in 64-bit (the hidden activations rounded where the part
+    rounds them, so that a token's choice of expert is the only thing rounding can flip)."""
+    def ln(x, pre):
+        return plain_phi.layer_norm(x, W[pre + ".weight"], W[pre + ".bias"], 1e-6)
+
+    def ffn(n, i):
+        nn = n.to(act_dtype).double()
+        p = torch.softmax(nn.float() @ W[f"h.{i}.ffn.router.weight"].float().T, -1).double()
+        gate, choice = p.max(-1)
+        up = W[f"h.{i}.ffn.up.weight"].reshape(cfg.experts, 24, cfg.hidden_size)
+        down = W[f"h.{i}.ffn.down.weight"].reshape(cfg.experts, cfg.hidden_size, 24)
+        out = torch.zeros_like(n)
+        for t in range(n.shape[0]):
+            e = int(choice[t])
+            h = torch.relu(nn[t] @ up[e].T).to(act_dtype).double()
+            out[t] = gate[t] * (h @ down[e].T)
+        return out
+
+    def att(n, i):
+        T = n.shape[0]
+        qkv = lambda k: n @ W[f"h.{i}.mixer.{k}.weight"].T + W[f"h.{i}.mixer.{k}.bias"]
+        q, k, v = (qkv(s).reshape(T, 2, 16) for s in "qkv")
+        half = 4
+        inv = 50.0 ** (-torch.arange(half, dtype=torch.float64) * 2 / 8)
+        ang = (torch.arange(T, dtype=torch.float64) / cfg.stretch)[:, None] * inv[None, :]
+        sin, cos = ang.sin(), ang.cos()
+        q, k = plain_phi.apply_rope(q, sin, cos, 8) * 0.25, plain_phi.apply_rope(k, sin, cos, 8)
+        return plain_phi.attention(q, k, v).reshape(T, 32) @ W[f"h.{i}.mixer.out.weight"].T + W[f"h.{i}.mixer.out.bias"]
+
+    x = W["emb.weight"][torch.tensor(tokens)]
+    n = ln(x, "h.0.norm")
+    x = (x + ffn(n, 0)) + att(n, 0)
+    x = x + att(ln(x, "h.1.norm"), 1)
+    x = x + ffn(ln(x, "h.1.norm2"), 1)
+    return ln(x, "norm_f") @ W["head.weight"].T + W["head.bias"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_position_registered_built_and_stepped(dtype):
+    import gopherllm_b200 as gl
+    arch = define_toy_routed()
+    cfg = arch.config_class()
+    folder = tempfile.mkdtemp(prefix="gl_toy_routed_")
+    gl.write_random_model(folder, cfg.to_dict(), seed=5)
+    m = gl.load(folder, dtype=dtype, max_tokens=512)
+    assert m.architecture.name == "toy-routed"
+    _, W = plain_phi.read_folder(folder)
+    rng = np.random.default_rng(6)
+    seqs = [tiny.prompt(rng, n, cfg.vocab_size) for n in (40, 9)]
+    act = torch.float32 if dtype == "float32" else torch.bfloat16
+    refs = [toy_routed_plain(s, W, cfg, act).numpy() for s in seqs]
+    tol = dict(float32=2e-4, bfloat16=3e-2)[dtype]
+    slots = [m.open_sequence() for _ in seqs]
+    cut = [25, 4]
+    out = m.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], [list(range(c)) for c in cut]).cpu().numpy()
+    # a token whose two best experts are nearly tied may go either way under rounding: compare the others
+    def close(got, ref):
+        return np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
+    rows, o, bad = 0, 0, 0
+    for i, c in enumerate(cut):
+        for t in range(c):
+            rows += 1
+            bad += not close(out[o + t], refs[i][t])
+        o += c
+    for t in range(max(len(s) - c for s, c in zip(seqs, cut))):
+        live = [i for i in range(2) if cut[i] + t < len(seqs[i])]
+        got = m.step([(slots[i], [seqs[i][cut[i] + t]]) for i in live]).cpu().numpy()
+        for r, i in enumerate(live):
+            rows += 1
+            bad += not close(got[r], refs[i][cut[i] + t])
+    for sl in slots:
+        m.close_sequence(sl)
+    assert bad == 0 if dtype == "float32" else bad <= rows // 10, (bad, rows)
