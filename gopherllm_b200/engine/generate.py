@@ -126,6 +126,10 @@ class SequenceState:
         self.fed = len(self.prompt)          # positions in the cache
         self.finish_reason: Optional[str] = None
 
+    def may_continue(self) -> bool:
+        """Whether a next token that is no stop token would be fed for another step."""
+        return len(self.generated) + 1 < self.max_tokens and self.fed < self.max_positions
+
     def accept(self, token: int) -> bool:
         """Take the sampled token; True if it must be fed for another step."""
         if self.finish_reason is not None:
@@ -151,6 +155,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
     batches = plan_batches([len(p) for p in prompts], options.max_tokens, spec.max_positions,
                            cache.n_pages, cache.max_slots)
     results: List[Optional[GenerationResult]] = [None] * len(prompts)
+    prepare = getattr(engine, "prepare_decode", None)
     for batch in batches:
         t_start = time.perf_counter()
         states = [SequenceState(prompts[i], options.max_tokens, options.stop_tokens, spec.max_positions)
@@ -169,7 +174,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
             while live:
                 if rows_dev is None:
                     rows_dev = torch.tensor(live, dtype=torch.int32).to(engine.device)
-                tokens = sampler.sample(logits, rows_dev).tolist()      # waits for the step
+                chosen = sampler.sample(logits, rows_dev)
+                # While the device finishes the step and samples: the next step's descriptor, if every
+                # sequence can go on (the tokens are filled in when they are known).
+                ahead = None
+                if prepare is not None and all(states[r].may_continue() for r in live):
+                    ahead = prepare([slots[r] for r in live])
+                tokens = chosen.tolist()                                # waits for the step
                 now = time.perf_counter()
                 if first:
                     t_prefill_end = now
@@ -194,7 +205,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                     canceled = True
                     break
                 if runs:
-                    logits = engine.step(runs)
+                    if ahead is not None and len(runs) == len(tokens):
+                        logits = engine.finish_decode(ahead, tokens)
+                    else:
+                        logits = engine.step(runs)
         finally:
             for s in slots:
                 if s is not None:

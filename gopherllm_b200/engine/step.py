@@ -195,7 +195,28 @@ class Engine:
         (default: the last token of every run).  Returns float32 [wanted, vocab] on
         the device, in the order of runs and of want."""
         lay, buf, meta = self.plan(runs, want)
-        pin = self._stage(buf)
+        return self._launch(lay, self._stage(buf), meta)
+
+    def prepare_decode(self, slots: Sequence[int]):
+        """The host's share of a one-token step that does not depend on the tokens themselves:
+        page reservation, positions, page tables, the staged descriptor.  A generation loop calls
+        this while the device still works on the step before, then ``finish_decode`` with the
+        sampled tokens; a handle that is not finished (the batch changed) is simply dropped."""
+        lay, buf, meta = self.plan([(s, (0,)) for s in slots], None)
+        return lay, self._stage(buf), meta
+
+    def finish_decode(self, handle, tokens: Sequence[int]) -> torch.Tensor:
+        lay, pin, meta = handle
+        toks = np.asarray(tokens, dtype=np.int64)
+        o, n = lay.off["tokens"]
+        if toks.shape != (n,):
+            raise ValueError(f"{n} tokens expected, one per sequence")
+        if toks.min() < 0 or toks.max() >= self.vocab:
+            raise ValueError(f"token id outside [0, {self.vocab})")
+        pin.numpy()[o:o + n] = toks
+        return self._launch(lay, pin, meta)
+
+    def _launch(self, lay: _Layout, pin: torch.Tensor, meta: dict) -> torch.Tensor:
         graph = None
         if self.use_graphs and meta["is_decode"] and lay.B <= self.graph_max_batch:
             graph = self._decode_graph(lay, meta)
@@ -205,7 +226,7 @@ class Engine:
             graph.graph.replay()
             logits = graph.logits
         else:
-            dev = torch.empty(buf.size, dtype=torch.int32, device=self.device)
+            dev = torch.empty(lay.size, dtype=torch.int32, device=self.device)
             dev.copy_(pin, non_blocking=True)
             self._staged_done()
             logits = self.model.forward(self.context(lay, dev, meta), self.cache)
