@@ -70,13 +70,19 @@ struct TgWork {
 __device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) { return umma_tile_desc(smem_addr, 128); }
 __host__ __device__ constexpr uint32_t umma_idesc(int bn) { return umma_idesc_bf16(bn, 0); }
 
-template <int BN, int STAGES, typename TO>
+// MT: 128-row sub-tiles of a block's tile (1 or 2).  With 2, the block's two products of a k-step share
+// the weight tile in shared memory, which cuts the operand bytes pulled from L2 per flop: at these tile
+// sizes L2 bandwidth, not the tensor pipe, sets the pace.  The accumulators then fill tensor memory
+// (no second set), so a tile's epilogue is not hidden behind the next tile's products.
+template <int BN, int STAGES, typename TO, int MT>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, int out_mode, int split) {
     extern __shared__ unsigned char smem_raw[];
-    constexpr int A_BYTES = TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
-    constexpr unsigned TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);   // a power of two holding both accumulators
+    constexpr int A_BYTES = MT * TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
+    constexpr int NBUF = 2 * MT * BN <= 512 ? 2 : 1;                                      // accumulator sets
+    static_assert(MT * BN <= 512, "the accumulators of a tile must fit tensor memory");
+    constexpr unsigned TMEM_COLS = NBUF * MT * BN <= 128 ? 128 : (NBUF * MT * BN <= 256 ? 256 : 512);   // a power of two
     __shared__ unsigned tmem_base_slot;
     __shared__ volatile int failed;
 
@@ -87,14 +93,14 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     const unsigned bar_tfull = bar_empty + 8 * STAGES;        // [2] accumulator ready for the epilogue
     const unsigned bar_tempty = bar_tfull + 16;               // [2] accumulator drained
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = (g.M + TG_BM - 1) / TG_BM, tiles_n = (g.N + BN - 1) / BN;
+    const int tiles_m = (g.M + MT * TG_BM - 1) / (MT * TG_BM), tiles_n = (g.N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
     const int k_blocks = (g.K + TG_BK - 1) / TG_BK;
 
     if (threadIdx.x == 0) {
         failed = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 4); }
+        for (int b = 0; b < NBUF; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, 4); }
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -113,13 +119,15 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             int it = 0, tile, kb0, kb1;
             TgWork work(n_tiles, k_blocks, split);
             while (!failed && work.next(tile, kb0, kb1)) {
-                const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+                const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m) * BN;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1)) { failed = 1; break; }
                     const unsigned sb = base + s * STAGE;
                     mbar_expect_tx(bar_full + 8 * s, STAGE);
-                    tma_load_2d(sb, &map_a, kb * TG_BK, m0, bar_full + 8 * s);
+#pragma unroll
+                    for (int i = 0; i < MT; ++i)
+                        tma_load_2d(sb + i * TG_BM * 128, &map_a, kb * TG_BK, m0 + i * TG_BM, bar_full + 8 * s);
                     tma_load_2d(sb + A_BYTES, &map_w, kb * TG_BK, n0, bar_full + 8 * s);
                 }
             }
@@ -131,19 +139,23 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             int it = 0, local = 0, tile, kb0, kb1;
             TgWork work(n_tiles, k_blocks, split);
             for (; !failed && work.next(tile, kb0, kb1); ++local) {
-                const int buf = local & 1;
-                if (local >= 2 && !mbar_wait(bar_tempty + 8 * buf, ((local >> 1) - 1) & 1)) { failed = 1; break; }
+                const int buf = local % NBUF, use = local / NBUF;
+                if (use >= 1 && !mbar_wait(bar_tempty + 8 * buf, (use - 1) & 1)) { failed = 1; break; }
                 tc_fence_after();
-                const unsigned d = tmem_base + buf * BN;
+                const unsigned d = tmem_base + buf * MT * BN;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(bar_full + 8 * s, (it / STAGES) & 1)) { failed = 1; break; }
                     tc_fence_after();
                     const unsigned sb = base + s * STAGE;
-                    const uint64_t da = umma_desc(sb), db = umma_desc(sb + A_BYTES);
+                    const uint64_t db = umma_desc(sb + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TG_BK / 16; ++k)     // 32 bytes further along the swizzled row per K 16
-                        umma_bf16(d, da + 2 * k, db + 2 * k, idesc, kb != kb0 || k != 0);
+                    for (int i = 0; i < MT; ++i) {
+                        const uint64_t da = umma_desc(sb + i * TG_BM * 128);
+#pragma unroll
+                        for (int k = 0; k < TG_BK / 16; ++k)     // 32 bytes further along the swizzled row per K 16
+                            umma_bf16(d + i * BN, da + 2 * k, db + 2 * k, idesc, kb != kb0 || k != 0);
+                    }
                     umma_commit(bar_empty + 8 * s);          // the stage is free once these products have read it
                 }
                 if (failed) break;
@@ -166,16 +178,19 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         TO* O = (TO*)g.out;
         TgWork work(n_tiles, k_blocks, split);
         for (; work.next(tile, kb0, kb1); ++local) {
-            const int buf = local & 1;
-            const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * BN;
+            const int buf = local % NBUF, use = local / NBUF;
+            const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m) * BN;
             // before the accumulator is ready: this tile's bias into shared memory
+            __syncwarp();
             for (int j = lane; j < BN; j += 32) bias_s[j] = (g.bias && kb0 == 0 && n0 + j < g.N) ? g.bias[n0 + j] : 0.f;
-            bool ok = mbar_wait(bar_tfull + 8 * buf, (local >> 1) & 1);
+            bool ok = mbar_wait(bar_tfull + 8 * buf, use & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { failed = 1; break; }
             tc_fence_after();
-            const int mrow0 = m0 + quarter * 32;
-            const unsigned trow = tmem_base + buf * BN + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int sub = 0; sub < MT; ++sub) {
+            const int mrow0 = m0 + sub * TG_BM + quarter * 32;
+            const unsigned trow = tmem_base + (buf * MT + sub) * BN + ((unsigned)(quarter * 32) << 16);
             // out_mode 1: tile store by TMA; 2: add-reduction by TMA; 0: element-wise (any alignment,
             // tensors to add that are not the output)
             constexpr int CW = sizeof(TO) == 4 ? 32 : 64;              // columns per 128-byte patch row
@@ -240,6 +255,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     }
                 }
             }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
@@ -255,10 +271,10 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     if (threadIdx.x == 0 && failed) atomicExch(&gl_wait_failed, 1);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 static constexpr size_t tg_smem() {
     // stages, 1024 bytes of barriers, the epilogue warps' patches and bias rows, room to align the start
-    return (size_t)STAGES * (TG_BM * 128 + BN * 128) + 1024 + 4 * 5120 + 4 * BN * 4 + 1024;
+    return (size_t)STAGES * (MT * TG_BM * 128 + BN * 128) + 1024 + 4 * 5120 + 4 * BN * 4 + 1024;
 }
 
 // 0 (the default) never cuts tiles: inside a model step, where the products run back to back at the
@@ -268,13 +284,14 @@ static constexpr size_t tg_smem() {
 static int tg_split_mode = 0;
 GL_API void gl_gemm_tcgen05_set_split(int mode) { tg_split_mode = mode; }
 
-template <int BN, int STAGES, typename TO>
+template <int BN, int STAGES, typename TO, int MT = 1>
 static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
-    constexpr size_t smem = tg_smem<BN, STAGES>();
+    constexpr size_t smem = tg_smem<BN, STAGES, MT>();
+    static_assert(smem <= 227 * 1024, "shared memory of a block");
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
-        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, TO, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess) {
             cudaGetLastError();
             return GL_ERR_SMEM;
@@ -307,7 +324,7 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
         rc = gl_cached_map(&map_out, g.out, (uint64_t)g.M, (uint64_t)g.N, 32, sizeof(TO) == 4 ? 32 : 64, (uint32_t)sizeof(TO));
         if (rc != GL_OK) return rc;
     }
-    const int tiles = ((g.M + TG_BM - 1) / TG_BM) * ((g.N + BN - 1) / BN);
+    const int tiles = ((g.M + MT * TG_BM - 1) / (MT * TG_BM)) * ((g.N + BN - 1) / BN);
     // Tiles that fill the SMs unevenly are cut where the blocks' equal shares meet, if the epilogue can
     // add parts onto the output and every share still holds a fair run of k-blocks.
     const int k_blocks = (g.K + TG_BK - 1) / TG_BK;
@@ -317,7 +334,7 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     const bool can_split = out_mode == 2 && g.act == GL_ACT_NONE && (long long)tiles * k_blocks >= 8LL * sms;
     const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64));
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
-    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_out, out_mode, split);
+    gemm_tcgen05_kernel<BN, STAGES, TO, MT><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_out, out_mode, split);
     return gl_check_launch();
 }
 
@@ -328,6 +345,10 @@ static int dispatch_bn(const GemmArgs& g, int bn, cudaStream_t stream) {
     if (bn == 128) return launch_tg<128, 6, TO>(g, stream);
     if (bn == 64) return launch_tg<64, 8, TO>(g, stream);
     if (bn == 160 && sizeof(TO) == 4) return launch_tg<160, 5, TO>(g, stream);    // 160 is no multiple of 64: 32-bit outputs only
+    // 1000 + width: tiles of 256 rows
+    if (bn == 1256) return launch_tg<256, 3, TO, 2>(g, stream);
+    if (bn == 1192) return launch_tg<192, 3, TO, 2>(g, stream);
+    if (bn == 1160 && sizeof(TO) == 4) return launch_tg<160, 3, TO, 2>(g, stream);
     return GL_ERR_SHAPE;
 }
 
@@ -365,6 +386,13 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
             const long cost = (long)((tiles + sms - 1) / sms) * (TG_BM + c);
             if (best < 0 || cost < best) { best = cost; bn = c; }
         }
+        // A long product added onto its 32-bit output, many rows, few columns (the second feed-forward
+        // product): tiles of 256 x 160 when one wave of them covers the output.  Two products of a
+        // k-step then share the weight tile (81 instead of 112 bytes from L2 per clock of tensor work);
+        // measured 108 against 127 us at 2048 x 2560 x 10240.  Shorter products gain nothing from it.
+        if (out_dtype == GL_F32 && g.add0 == (const float*)g.out && !g.add1 && g.K >= 5120 && g.M > 128 &&
+            ((g.M + 255) / 256) * ((g.N + 159) / 160) <= sms)
+            bn = 1160;
     }
     if (out_dtype == GL_F32) return dispatch_bn<float>(g, bn, stream);
     if (out_dtype == GL_BF16) return dispatch_bn<__nv_bfloat16>(g, bn, stream);

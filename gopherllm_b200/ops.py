@@ -463,8 +463,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[1] % 8:
         raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
-    if tile_n not in (0, 64, 128, 160, 192, 256):
-        raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256")
+    if tile_n not in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
+        raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256; "
+                          "1000 more for tiles of 256 rows (160, 192, 256)")
     fn = _lib("gemm_tcgen05.cu", _defines).gl_gemm_tcgen05
     _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(tile_n), _stream()), "gemm_tcgen05")
     return out

@@ -86,18 +86,18 @@ def test_gemm_tcgen05(M, N, K):
     a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
     bias, add0, add1 = rnd(N, seed=2), rnd(M, N, seed=3), rnd(M, N, seed=4)
     ref = ref_linear(a, w, bias, "gelu_new", add0, add1)
-    for tile in (0, 64, 128, 160, 192, 256):
+    for tile in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
         got = o.gemm_tcgen05(a, w, bias, "gelu_new", add0, add1, out_dtype=torch.float32, tile_n=tile)
         torch.cuda.synchronize()
         assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
         err = (got.double() - ref).abs().max().item()
         assert err <= 3e-5 * max(1.0, ref.abs().max().item()), (tile, err)
     for act in (None, "gelu_new"):
-        for tile in (0, 64, 192):
+        for tile in (0, 64, 192, 1192, 1256):
             got = o.gemm_tcgen05(a, w, bias, act, out_dtype=torch.bfloat16, tile_n=tile)
             ref = ref_linear(a, w, bias, act, None, None)
             assert (got.double() - ref).abs().max() <= 2 ** -8 * max(1.0, ref.abs().max().item()), (act, tile)
-    for tile in (0, 160, 256):
+    for tile in (0, 160, 256, 1160, 1256):
         got = o.gemm_tcgen05(a, w, bias, "gelu", out_dtype=torch.float32, tile_n=tile)    # the plain TMA store
         ref = ref_linear(a, w, bias, "gelu", None, None)
         assert (got.double() - ref).abs().max() <= 3e-5 * max(1.0, ref.abs().max().item()), tile
@@ -105,12 +105,13 @@ def test_gemm_tcgen05(M, N, K):
     x = add0.clone()                                                   # in place on the residual stream
     o.gemm_tcgen05(a, w, bias, None, x, add1, out=x)
     assert (x.double() - ref_linear(a, w, bias, None, add0, add1)).abs().max() <= 3e-5 * max(1.0, ref.abs().max().item())
-    x = add0.clone()                                                   # out = out + product: the add-reduction path
-    o.gemm_tcgen05(a, w, bias, "relu", x, out=x)
-    torch.cuda.synchronize()
-    assert o.wait_failures()["gemm_tcgen05.cu"] == 0
     want = ref_linear(a, w, bias, "relu", add0, None)
-    assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
+    for tile in (0, 1160, 1256):
+        x = add0.clone()                                               # out = out + product: the add-reduction path
+        o.gemm_tcgen05(a, w, bias, "relu", x, out=x, tile_n=tile)
+        torch.cuda.synchronize()
+        assert o.wait_failures()["gemm_tcgen05.cu"] == 0
+        assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item()), tile
 
 
 @pytest.mark.parametrize("M,N,K", [(1024, 2560, 1024), (520, 1300, 4104), (2048, 2560, 2560)])
@@ -129,7 +130,7 @@ def test_gemm_tcgen05_cut_tiles(M, N, K):
 
 
 def _cut_tiles_checks(o, a, w, bias, x0, want, M, N, K):
-    for tile in (0, 128, 256):
+    for tile in (0, 128, 256, 1160):
         x = x0.clone()
         o.gemm_tcgen05(a, w, bias, None, x, out=x, tile_n=tile)
         torch.cuda.synchronize()
@@ -156,7 +157,7 @@ def test_gemm_tcgen05_one_weight_stands_out():
     for (n, k) in [(0, 0), (519, 1095), (77, 1029), (256, 63), (255, 64), (128, 15), (127, 16), (511, 1088)]:
         w = torch.zeros(N, K, dtype=torch.bfloat16, device=DEV)
         w[n, k] = 3.0
-        for tile in (64, 128, 160, 192, 256):
+        for tile in (64, 128, 160, 192, 256, 1160, 1192, 1256):
             got = o.gemm_tcgen05(a, w, out_dtype=torch.float32, tile_n=tile)
             want = torch.zeros(M, N, device=DEV)
             want[:, n] = 3.0
@@ -166,10 +167,11 @@ def test_gemm_tcgen05_one_weight_stands_out():
     for (m, k) in [(0, 0), (129, 1095), (64, 520), (127, 7), (128, 8)]:
         a = torch.zeros(M, K, dtype=torch.bfloat16, device=DEV)
         a[m, k] = 2.0
-        got = o.gemm_tcgen05(a, w, out_dtype=torch.float32)
-        want = torch.zeros(M, N, device=DEV)
-        want[m, :] = 2.0
-        assert torch.equal(got, want), (m, k)
+        for tile in (0, 1192):
+            got = o.gemm_tcgen05(a, w, out_dtype=torch.float32, tile_n=tile)
+            want = torch.zeros(M, N, device=DEV)
+            want[m, :] = 2.0
+            assert torch.equal(got, want), (m, k, tile)
 
 
 def test_gemm_skinny_one_weight_stands_out():
