@@ -65,6 +65,7 @@ class GenerationStats:
     prefill_time: float = 0.0
     decode_time: float = 0.0
     total_time: float = 0.0
+    token_times: List[float] = field(default_factory=list)   # seconds from the request's start to each token
 
 
 @dataclass
@@ -190,6 +191,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                     first = False
                 nxt, runs = [], []
                 for r, tok in zip(live, tokens):
+                    stats[r].token_times.append(now - t_start)
                     if states[r].accept(tok):
                         nxt.append(r)
                         runs.append((slots[r], [tok]))

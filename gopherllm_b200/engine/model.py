@@ -94,11 +94,23 @@ class DecoderModel:
     # -- compute ------------------------------------------------------------
     def forward(self, ctx, cache) -> torch.Tensor:
         """Run the step described by ctx; float32 logits [len(ctx.want_rows), vocab]."""
-        s = self.spec
-        x = ops.embed(self.embedding, ctx.tokens, s.embedding_scale)
-        for e in s.schedule:
+        x = self.begin(ctx)
+        self.run(x, ctx, cache, 0, len(self.spec.schedule))
+        return self.finish(x, ctx)
+
+    # The same step in three pieces, for a caller that captures it as more than one CUDA graph.
+    def begin(self, ctx) -> torch.Tensor:
+        """The residual stream of the step's tokens, float32 [tokens, hidden]."""
+        return ops.embed(self.embedding, ctx.tokens, self.spec.embedding_scale)
+
+    def run(self, x, ctx, cache, start: int, stop: int) -> None:
+        """Runs start..stop-1 of the schedule, updating x in place."""
+        for e in self.spec.schedule[start:stop]:
             view = cache.view(e.cache, e.writes) if e.cache is not None else None
             self.blocks[e.layer].forward(x, ctx, view)
+
+    def finish(self, x, ctx) -> torch.Tensor:
+        s = self.spec
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab), dtype=torch.float32, device=x.device)
         xn = self.final_norm.forward(x, ctx.act_dtype, rows=ctx.want_rows)

@@ -80,6 +80,7 @@ class Engine:
         # batch shape; the 32-bit path always launches kernel by kernel
         self.use_graphs = act_dtype == torch.bfloat16 and bool(getattr(model, "capturable", False))
         self.graph_max_batch = 256
+        self.graph_first_runs = 2                            # runs of the schedule in a step's first, short graph
         self._graphs: Dict[tuple, object] = {}
         self._graph_pool = None
         self.overlap_branches = True                         # decode steps run parallel branches on two streams
@@ -223,7 +224,9 @@ class Engine:
         if graph is not None:
             graph.desc.copy_(pin, non_blocking=True)
             self._staged_done()
-            graph.graph.replay()
+            graph.first.replay()
+            if graph.graph is not None:
+                graph.graph.replay()
             logits = graph.logits
         else:
             dev = torch.empty(lay.size, dtype=torch.int32, device=self.device)
@@ -252,11 +255,27 @@ class Engine:
             bound["new_lens"] = [self.cache.max_positions]      # launch sizes must hold for any length
             ctx = self.context(lay, g.desc, bound)
             torch.cuda.synchronize(self.device)
-            g.graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
-            with torch.cuda.graph(g.graph, pool=self._graph_pool):
-                g.logits = self.model.forward(ctx, self.cache)
+            # Two graphs replayed back to back: a short one (the embedding and the first runs of the
+            # schedule) that the device can start soon after the launch call, and the rest, whose
+            # longer launch is then hidden behind the first one's work.  A step that is launched from
+            # an idle device (the generation loop waits for each step's tokens) otherwise pays the
+            # whole launch of a few hundred nodes before its first kernel.
+            n_runs = len(self.model.spec.schedule)
+            n_first = min(self.graph_first_runs, n_runs)
+            g.first = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g.first, pool=self._graph_pool):
+                g.x = self.model.begin(ctx)
+                self.model.run(g.x, ctx, self.cache, 0, n_first)
+                if n_first == n_runs:
+                    g.logits = self.model.finish(g.x, ctx)
+            g.graph = None
+            if n_first < n_runs:
+                g.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g.graph, pool=self._graph_pool):
+                    self.model.run(g.x, ctx, self.cache, n_first, n_runs)
+                    g.logits = self.model.finish(g.x, ctx)
             self._graphs[key] = g
         return g
 
