@@ -22,6 +22,18 @@ def test_accept_order_stop_emit_length_feed():
     assert not s.accept(6) and s.finish_reason == "length" and s.generated == [5, 6]
 
 
+def test_may_continue_foretells_accept():
+    # the loop prepares the next step ahead only if every sequence would feed a token that is no stop token
+    for max_tokens in (1, 2, 3, 7):
+        for max_positions in (4, 5, 6, 50):
+            s = SequenceState([1, 2, 3], max_tokens=max_tokens, stop_tokens=[9], max_positions=max_positions)
+            while s.finish_reason is None:
+                told = s.may_continue()
+                assert s.accept(5) == told, (max_tokens, max_positions, s.generated)
+    s = SequenceState([1, 2, 3], max_tokens=5, stop_tokens=[9], max_positions=50)
+    assert s.may_continue() and not s.accept(9)           # a stop token ends it whatever was foretold
+
+
 def test_plan_batches():
     P = 64
     # worst-case pages: prompt + every token it may feed, capped by the longest sequence
