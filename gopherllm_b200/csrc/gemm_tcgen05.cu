@@ -33,6 +33,13 @@ struct GemmArgs {
     const float* add1;    // [M, N] or null
     void* out;            // [M, N] f32 or bf16
     int M, N, K, act;
+    // a second product summed into the same tile (out = act(a w^T + a2 w2^T + bias + bias2) + ...): two
+    // branches that end on the same rows and columns cost one epilogue.  The second product starts on a
+    // k-block of its own (what the first one's last block lacks is zero-filled by TMA).
+    const void* a2;       // [M, K2] bf16 or null
+    const void* w2;       // [N, K2] bf16
+    const float* bias2;   // [N] or null
+    int K2;
 };
 
 // The work of one block: whole output tiles taken round-robin, or (split) an equal share of all
@@ -77,6 +84,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(int bn) { return umma_idesc_bf
 template <int BN, int STAGES, typename TO, int MT>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_w2,
                     const __grid_constant__ CUtensorMap map_out, int out_mode, int split) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int A_BYTES = MT * TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
@@ -95,7 +103,8 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (g.M + MT * TG_BM - 1) / (MT * TG_BM), tiles_n = (g.N + BN - 1) / BN;
     const int n_tiles = tiles_m * tiles_n;
-    const int k_blocks = (g.K + TG_BK - 1) / TG_BK;
+    const int k1_blocks = (g.K + TG_BK - 1) / TG_BK;                   // k-blocks of the first product
+    const int k_blocks = k1_blocks + (g.a2 ? (g.K2 + TG_BK - 1) / TG_BK : 0);
 
     if (threadIdx.x == 0) {
         failed = 0;
@@ -125,10 +134,14 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1)) { failed = 1; break; }
                     const unsigned sb = base + s * STAGE;
                     mbar_expect_tx(bar_full + 8 * s, STAGE);
+                    const bool second = kb >= k1_blocks;
+                    const CUtensorMap* ma = second ? &map_a2 : &map_a;
+                    const CUtensorMap* mw = second ? &map_w2 : &map_w;
+                    const int k0 = (second ? kb - k1_blocks : kb) * TG_BK;
 #pragma unroll
                     for (int i = 0; i < MT; ++i)
-                        tma_load_2d(sb + i * TG_BM * 128, &map_a, kb * TG_BK, m0 + i * TG_BM, bar_full + 8 * s);
-                    tma_load_2d(sb + A_BYTES, &map_w, kb * TG_BK, n0, bar_full + 8 * s);
+                        tma_load_2d(sb + i * TG_BM * 128, ma, k0, m0 + i * TG_BM, bar_full + 8 * s);
+                    tma_load_2d(sb + A_BYTES, mw, k0, n0, bar_full + 8 * s);
                 }
             }
         }
@@ -182,7 +195,14 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m) * BN;
             // before the accumulator is ready: this tile's bias into shared memory
             __syncwarp();
-            for (int j = lane; j < BN; j += 32) bias_s[j] = (g.bias && kb0 == 0 && n0 + j < g.N) ? g.bias[n0 + j] : 0.f;
+            for (int j = lane; j < BN; j += 32) {
+                float bv = 0.f;
+                if (kb0 == 0 && n0 + j < g.N) {
+                    if (g.bias) bv = g.bias[n0 + j];
+                    if (g.bias2) bv += g.bias2[n0 + j];
+                }
+                bias_s[j] = bv;
+            }
             bool ok = mbar_wait(bar_tfull + 8 * buf, use & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { failed = 1; break; }
@@ -307,6 +327,13 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     if (rc != GL_OK) return rc;
     rc = gl_cached_map_bf16(&map_w, g.w, (uint64_t)g.N, (uint64_t)g.K, BN, TG_BK);
     if (rc != GL_OK) return rc;
+    CUtensorMap map_a2 = map_a, map_w2 = map_w;
+    if (g.a2) {
+        rc = gl_cached_map_bf16(&map_a2, g.a2, (uint64_t)g.M, (uint64_t)g.K2, TG_BM, TG_BK);
+        if (rc != GL_OK) return rc;
+        rc = gl_cached_map_bf16(&map_w2, g.w2, (uint64_t)g.N, (uint64_t)g.K2, BN, TG_BK);
+        if (rc != GL_OK) return rc;
+    }
     // How results leave: by TMA when the output's rows are whole 16-byte units and nothing has to be
     // loaded: a plain store when nothing is added, an add-reduction for out = out + product (add0
     // is the output itself, 32-bit); otherwise element by element.
@@ -327,14 +354,14 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     const int tiles = ((g.M + MT * TG_BM - 1) / (MT * TG_BM)) * ((g.N + BN - 1) / BN);
     // Tiles that fill the SMs unevenly are cut where the blocks' equal shares meet, if the epilogue can
     // add parts onto the output and every share still holds a fair run of k-blocks.
-    const int k_blocks = (g.K + TG_BK - 1) / TG_BK;
+    const int k_blocks = (g.K + TG_BK - 1) / TG_BK + (g.a2 ? (g.K2 + TG_BK - 1) / TG_BK : 0);
     const int waves = (tiles + sms - 1) / sms;
     const bool uneven = tiles % sms != 0 && (long long)tiles * 100 < (long long)waves * sms * 92;
     // (alone it pays only for a long K: a cut tile costs a second add-reduction of its 32-bit patch)
     const bool can_split = out_mode == 2 && g.act == GL_ACT_NONE && (long long)tiles * k_blocks >= 8LL * sms;
     const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64));
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
-    gemm_tcgen05_kernel<BN, STAGES, TO, MT><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_out, out_mode, split);
+    gemm_tcgen05_kernel<BN, STAGES, TO, MT><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_a2, map_w2, map_out, out_mode, split);
     return gl_check_launch();
 }
 
@@ -364,6 +391,12 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
     if (g.M <= 0 || g.N <= 0) return GL_OK;
     if (g.K <= 0 || g.K % 8) return GL_ERR_SHAPE;
     if (((uintptr_t)g.a | (uintptr_t)g.w) & 15) return GL_ERR_ALIGN;
+    if (g.a2) {
+        // the second product starts on a k-block of its own: a partial last block of the first would
+        // be padded with zeros by TMA, which is fine, but K2 still needs whole 16-byte rows
+        if (!g.w2 || g.K2 <= 0 || g.K2 % 8) return GL_ERR_SHAPE;
+        if (((uintptr_t)g.a2 | (uintptr_t)g.w2) & 15) return GL_ERR_ALIGN;
+    }
     if (bn == 0) {
         // A tile's time goes with the operand bytes it pulls from L2, about (128 + width); the
         // grid runs in waves of one tile per SM, and the last wave counts whole.
@@ -390,7 +423,7 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
         // product): tiles of 256 x 160 when one wave of them covers the output.  Two products of a
         // k-step then share the weight tile (81 instead of 112 bytes from L2 per clock of tensor work);
         // measured 108 against 127 us at 2048 x 2560 x 10240.  Shorter products gain nothing from it.
-        if (out_dtype == GL_F32 && g.add0 == (const float*)g.out && !g.add1 && g.K >= 5120 && g.M > 128 &&
+        if (out_dtype == GL_F32 && g.add0 == (const float*)g.out && !g.add1 && g.K + (g.a2 ? g.K2 : 0) >= 5120 && g.M > 128 &&
             ((g.M + 255) / 256) * ((g.N + 159) / 160) <= sms)
             bn = 1160;
     }

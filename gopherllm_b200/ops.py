@@ -386,7 +386,10 @@ def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads
 class _GemmArgs(Structure):
     _fields_ = [("a", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("add0", c_void_p),
                 ("add1", c_void_p), ("out", c_void_p),
-                ("M", c_int), ("N", c_int), ("K", c_int), ("act", c_int)]
+                ("M", c_int), ("N", c_int), ("K", c_int), ("act", c_int),
+                # a second product summed into the same output (the tcgen05 kernel reads these; the
+                # other kernels' argument structs end before them)
+                ("a2", c_void_p), ("w2", c_void_p), ("bias2", c_void_p), ("K2", c_int)]
 
 
 def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
@@ -405,7 +408,7 @@ def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
     if act not in ACTIVATIONS:
         raise KernelError(f"activation {act!r} unknown")
     return _GemmArgs(a.data_ptr(), w.data_ptr(), _addr(bias), _addr(add0), _addr(add1), out.data_ptr(),
-                     M, N, K, ACTIVATIONS[act])
+                     M, N, K, ACTIVATIONS[act], None, None, None, 0)
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
@@ -453,9 +456,11 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
                  add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
-                 tile_n: int = 0, _defines=()) -> torch.Tensor:
+                 tile_n: int = 0, _defines=(), second=None) -> torch.Tensor:
     """The tensor-core product (tcgen05.mma fed by TMA, accumulators in tensor memory) for
-    bfloat16 operands with K a multiple of 8; meant for many rows."""
+    bfloat16 operands with K a multiple of 8; meant for many rows.  ``second`` = (a2, w2, bias2)
+    sums another product over the same rows and columns into the tile before the epilogue:
+    out = act(a·wᵀ + a2·w2ᵀ + bias + bias2) + add0 + add1."""
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     if out is None:
@@ -463,6 +468,15 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[1] % 8:
         raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
+    if second is not None:
+        a2, w2, bias2 = second
+        _need(a2, "a2", torch.bfloat16)
+        _need(w2, "w2", torch.bfloat16)
+        if a2.shape[0] != a.shape[0] or w2.shape[0] != w.shape[0] or a2.shape[1] != w2.shape[1] or a2.shape[1] % 8:
+            raise KernelError(f"second product [{tuple(a2.shape)}] x [{tuple(w2.shape)}] does not fit the first")
+        if bias2 is not None:
+            _need(bias2, "bias2", torch.float32, (w.shape[0],))
+        g.a2, g.w2, g.bias2, g.K2 = a2.data_ptr(), w2.data_ptr(), _addr(bias2), a2.shape[1]
     if tile_n not in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
         raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256; "
                           "1000 more for tiles of 256 rows (160, 192, 256)")
@@ -480,6 +494,20 @@ def wait_failures() -> dict:
         if "attention_prefill_tc" in key:
             out[key] = int(lib.gl_attention_prefill_tc_wait_failed())
     return out
+
+
+def linear_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                a2: torch.Tensor, w2: torch.Tensor, bias2: Optional[torch.Tensor],
+                add0: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = a·wᵀ + bias + a2·w2ᵀ + bias2 + add0: the last products of two branches that are added
+    to the same rows.  With many bfloat16 rows both run as one tensor-core product over the joined K
+    (one pass over the output instead of two); otherwise one after the other, each adding onto out."""
+    if (USE_TCGEN05 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a2.dtype == torch.bfloat16
+            and w2.dtype == torch.bfloat16 and a.shape[0] > SKINNY_MAX_ROWS and a.shape[1] % 8 == 0
+            and a2.shape[1] % 8 == 0):
+        return gemm_tcgen05(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
+    out = linear(a, w, bias, add0=add0, out_dtype=torch.float32, out=out)
+    return linear(a2, w2, bias2, add0=out, out=out)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,

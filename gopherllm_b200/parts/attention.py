@@ -67,6 +67,17 @@ class Attention(Mixer):
 
     # -- compute ----------------------------------------------------------
     def forward(self, xn, ctx, cache, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+        if len(add) > 2:
+            raise ValueError("at most two tensors can be added in the projection's epilogue")
+        o, w, b = self.until_last(xn, ctx, cache)
+        add = [a() if callable(a) else a for a in add]
+        a0 = add[0] if len(add) > 0 else None
+        a1 = add[1] if len(add) > 1 else None
+        return ops.linear(o, w, b, add0=a0, add1=a1, out=out)
+
+    def until_last(self, xn, ctx, cache):
+        """Everything but the output projection: the attention output [T, heads * head size] with the
+        projection's weight and bias."""
         s = self.spec
         T = xn.shape[0]
         qkv = ops.linear(xn, self.w_qkv, self.b_qkv, out_dtype=ctx.act_dtype)
@@ -86,12 +97,8 @@ class Attention(Mixer):
         o = torch.empty_like(q)
         ops.attention(q, o, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads,
                       s.head_dim, window=s.window)
-        if len(add) > 2:
-            raise ValueError("at most two tensors can be added in the projection's epilogue")
-        add = [a() if callable(a) else a for a in add]
-        a0 = add[0] if len(add) > 0 else None
-        a1 = add[1] if len(add) > 1 else None
-        return ops.linear(o, self.w_out, self.b_out, add0=a0, add1=a1, out=out)
+        return o, self.w_out, self.b_out
+
 
 
 register_mixer("attention", Attention)

@@ -96,6 +96,10 @@ class Mixer(Part):
     def cache_request(self):
         return None
 
+    # Optional: ``until_last(xn, ctx, cache)`` -> (activations, weight, bias), everything but the last
+    # product, for a block that runs the last products of its branches as one (ops.linear_pair).
+    until_last = None
+
     # A mixer that sets this accepts callables among ``add``: it calls them just before its last
     # product and adds what they return.  A block uses that to let another branch run beside the
     # mixer on a second stream and join only where its result is needed.
@@ -106,7 +110,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """forward(xn, ctx, add, out): out = ffn(xn) + sum(add), float32 [T, hidden]."""
+    """forward(xn, ctx, add, out): out = ffn(xn) + sum(add), float32 [T, hidden].
+    Optional: until_last(xn, ctx) -> (activations, weight, bias), everything but the last product."""
+
+    until_last = None
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

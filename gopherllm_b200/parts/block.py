@@ -5,6 +5,7 @@ from typing import Dict
 
 import torch
 
+from .. import ops
 from ..config.specs import BlockSpec
 from .base import Block, ParamSpec, build_feed_forward, build_mixer, build_norm, register_block
 
@@ -49,6 +50,13 @@ class ParallelBlock(_AssembledBlock):
     def forward(self, x, ctx, cache):
         xn = self.norm.forward(x, ctx.act_dtype)
         side = getattr(ctx, "side_stream", None)
+        if side is None and self.ffn.until_last is not None and self.mixer.until_last is not None:
+            # the branches' last products end on the same rows and columns: one product over the joined
+            # K where the kernels can (one pass over the residual stream), else one after the other
+            h, w2, b2 = self.ffn.until_last(xn, ctx)
+            o, wo, bo = self.mixer.until_last(xn, ctx, cache)
+            ops.linear_pair(h, w2, b2, o, wo, bo, add0=x, out=x)
+            return x
         if side is None or not self.mixer.deferred_add:
             # each branch adds itself onto the residual stream in its last product's epilogue,
             # the feed-forward first: (x + mlp) + attn, the reference's order

@@ -35,6 +35,10 @@ class DenseFeedForward(FeedForward):
         self.w_up, self.w_down = t["up.weight"], t["down.weight"]
         self.b_up, self.b_down = t.get("up.bias"), t.get("down.bias")
 
+    def until_last(self, xn, ctx):
+        h = ops.linear(xn, self.w_up, self.b_up, act=self.spec.activation, out_dtype=ctx.act_dtype)
+        return h, self.w_down, self.b_down
+
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         if len(add) > 2:
             raise ValueError("at most two tensors can be added in the projection's epilogue")

@@ -149,6 +149,32 @@ def _cut_tiles_checks(o, a, w, bias, x0, want, M, N, K):
         assert torch.equal(x, expect), (n, k)
 
 
+@pytest.mark.parametrize("M,N,K1,K2", [(300, 200, 96, 160), (130, 520, 200, 1096), (2048, 2560, 2560, 10240)])
+def test_gemm_tcgen05_two_products_one_tile(M, N, K1, K2):
+    """out = out + a1 w1^T + b1 + a2 w2^T + b2: two branches' last products as one product over the
+    joined K (K1 need not fill its last k-block), against the two run one after the other in 64-bit."""
+    o = ops()
+    a1, w1 = rnd(M, K1, dtype=torch.bfloat16), rnd(N, K1, dtype=torch.bfloat16, scale=0.05, seed=1)
+    a2, w2 = rnd(M, K2, dtype=torch.bfloat16, seed=5), rnd(N, K2, dtype=torch.bfloat16, scale=0.05, seed=6)
+    b1, b2, x0 = rnd(N, seed=2), rnd(N, seed=7), rnd(M, N, seed=3)
+    want = ref_linear(a1, w1, b1, None, x0, None) + ref_linear(a2, w2, b2, None, None, None)
+    for tile in (0, 128, 256, 1160):
+        x = x0.clone()
+        o.gemm_tcgen05(a1, w1, b1, None, x, out=x, tile_n=tile, second=(a2, w2, b2))
+        torch.cuda.synchronize()
+        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        err = (x.double() - want).abs().max().item()
+        assert err <= 3e-5 * max(1.0, want.abs().max().item()), (tile, err)
+    x = x0.clone()
+    o.linear_pair(a1, w1, b1, a2, w2, None, add0=x, out=x)                 # the dispatching call, one bias missing
+    want = ref_linear(a1, w1, b1, None, x0, None) + ref_linear(a2, w2, None, None, None, None)
+    assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
+    x = x0[:8].clone()                                                      # few rows: one after the other
+    o.linear_pair(a1[:8], w1, b1, a2[:8], w2, b2, add0=x, out=x)
+    want = ref_linear(a1[:8], w1, b1, None, x0[:8], None) + ref_linear(a2[:8], w2, b2, None, None, None)
+    assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
+
+
 def test_gemm_tcgen05_one_weight_stands_out():
     """A single large weight must reach exactly one output column, wherever it sits in K and N."""
     o = ops()
