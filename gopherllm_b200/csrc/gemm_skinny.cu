@@ -30,6 +30,12 @@ struct GemmArgs {
     const float* add1;    // [M, N] or null
     void* out;            // [M, N] f32 or bf16
     int M, N, K, act;
+    // a second product summed into the same output (out = act(a w^T + a2 w2^T + bias + bias2) + ...):
+    // K is then the joined length K1 + K2, with K1 a multiple of the stage's 64
+    const void* a2;       // [M, K2] bf16 or null
+    const void* w2;       // [N, K2] bf16
+    const float* bias2;   // [N] or null
+    int K2;
 };
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
@@ -52,7 +58,8 @@ __device__ __forceinline__ int swz(int r, int c) { return r * 128 + ((c ^ (r & 7
 template <int MT, int STAGES, typename TO>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensorMap map_w,
-                   const __grid_constant__ CUtensorMap map_a) {
+                   const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w2,
+                   const __grid_constant__ CUtensorMap map_a2) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int W_BYTES = SK_ROWS * 128, A_BYTES = MT * 8 * 128, STAGE = W_BYTES + A_BYTES;
     constexpr int LD = SK_ROWS + 1;
@@ -60,8 +67,9 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
     const int S = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.y * SK_ROWS;
+    const int k1 = g.K, k_all = g.K + (g.a2 ? g.K2 : 0);       // the first product's K, the joined K
     const int kb = blockIdx.x * k_per_block;
-    const int ke = min(g.K, kb + k_per_block);
+    const int ke = min(k_all, kb + k_per_block);
     const int iters = ke > kb ? (ke - kb + SK_BK - 1) / SK_BK : 0;
     // stages start on a 1024-byte boundary (the swizzle pattern repeats every 8 rows of 128 bytes)
     unsigned char* smem = smem_raw + ((1024u - (gl_smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -76,11 +84,15 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
     auto load_w = [&](int it) {                               // one thread: the stage's weights
         const unsigned sb = base + (it % STAGES) * STAGE, bar = bars + 8 * (it % STAGES);
         mbar_expect_tx(bar, STAGE);                           // the activations of the stage count too
-        tma_load_2d(sb, &map_w, kb + it * SK_BK, n0, bar);
+        const int k = kb + it * SK_BK;
+        if (k < k1) tma_load_2d(sb, &map_w, k, n0, bar);
+        else tma_load_2d(sb, &map_w2, k - k1, n0, bar);
     };
     auto load_a = [&](int it) {                               // one thread: the stage's activations
         const unsigned sb = base + (it % STAGES) * STAGE, bar = bars + 8 * (it % STAGES);
-        tma_load_2d(sb + W_BYTES, &map_a, kb + it * SK_BK, 0, bar);
+        const int k = kb + it * SK_BK;
+        if (k < k1) tma_load_2d(sb + W_BYTES, &map_a, k, 0, bar);
+        else tma_load_2d(sb + W_BYTES, &map_a2, k - k1, 0, bar);
     };
 
     float acc[MT][4];
@@ -148,6 +160,7 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
             v += peer[m * LD + nl];
         }
         if (g.bias) v += g.bias[n];
+        if (g.bias2) v += g.bias2[n];
         v = gl_activate<false>(v, g.act);
         const size_t o = (size_t)m * g.N + n;
         if (g.add0) v += g.add0[o];
@@ -176,15 +189,23 @@ static int launch_skinny(const GemmArgs& g, int S, cudaStream_t stream) {
         }
         configured = true;
     }
-    const int k_per_block = ((g.K + S - 1) / S + SK_BK - 1) / SK_BK * SK_BK;
+    const int k_all = g.K + (g.a2 ? g.K2 : 0);
+    const int k_per_block = ((k_all + S - 1) / S + SK_BK - 1) / SK_BK * SK_BK;
     CUtensorMap map_w, map_a;
     int rc = gl_cached_map_bf16(&map_w, g.w, (uint64_t)g.N, (uint64_t)g.K, SK_ROWS, SK_BK);
     if (rc != GL_OK) return rc;
     rc = gl_cached_map_bf16(&map_a, g.a, (uint64_t)g.M, (uint64_t)g.K, MT * 8, SK_BK);
     if (rc != GL_OK) return rc;
+    CUtensorMap map_w2 = map_w, map_a2 = map_a;
+    if (g.a2) {
+        rc = gl_cached_map_bf16(&map_w2, g.w2, (uint64_t)g.N, (uint64_t)g.K2, SK_ROWS, SK_BK);
+        if (rc != GL_OK) return rc;
+        rc = gl_cached_map_bf16(&map_a2, g.a2, (uint64_t)g.M, (uint64_t)g.K2, MT * 8, SK_BK);
+        if (rc != GL_OK) return rc;
+    }
     const dim3 grid(S, (g.N + SK_ROWS - 1) / SK_ROWS, 1);
     if (grid.y > 65535) return GL_ERR_SHAPE;
-    if (gl_launch(gemm_skinny_kernel<MT, STAGES, TO>, grid, dim3(SK_THREADS), smem, stream, S, g, k_per_block, map_w, map_a) != 0)
+    if (gl_launch(gemm_skinny_kernel<MT, STAGES, TO>, grid, dim3(SK_THREADS), smem, stream, S, g, k_per_block, map_w, map_a, map_w2, map_a2) != 0)
         return GL_ERR_LAUNCH;
     return GL_OK;
 }
@@ -218,6 +239,10 @@ GL_API int gl_gemm_skinny(const GemmArgs* args, int out_dtype, int split_k, cuda
     if (g.M <= 0 || g.N <= 0) return GL_OK;
     if (g.M > 64 || g.K <= 0 || g.K % 8) return GL_ERR_SHAPE;
     if (((uintptr_t)g.a | (uintptr_t)g.w) & 15) return GL_ERR_ALIGN;
+    if (g.a2) {
+        if (!g.w2 || g.K2 <= 0 || g.K2 % 8 || g.K % SK_BK) return GL_ERR_SHAPE;    // a stage lies in one product
+        if (((uintptr_t)g.a2 | (uintptr_t)g.w2) & 15) return GL_ERR_ALIGN;
+    }
     int S = split_k;
     if (S == 0) {
         static int sms = 0;
@@ -231,7 +256,8 @@ GL_API int gl_gemm_skinny(const GemmArgs* args, int out_dtype, int split_k, cuda
         const int tiles = (g.N + SK_ROWS - 1) / SK_ROWS;
         const int slots = sms * blocks_per_sm(g.M);
         S = 1;
-        while (S < 8 && tiles * S * 2 <= slots && g.K / (S * 2) >= 4 * SK_BK) S *= 2;
+        const int k_all = g.K + (g.a2 ? g.K2 : 0);
+        while (S < 8 && tiles * S * 2 <= slots && k_all / (S * 2) >= 4 * SK_BK) S *= 2;
     }
     if (S != 1 && S != 2 && S != 4 && S != 8) return GL_ERR_SHAPE;
     if (out_dtype == GL_F32) return dispatch_m<float>(g, S, stream);

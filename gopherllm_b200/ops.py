@@ -436,11 +436,24 @@ def gemm_tcgen05_cut_tiles(mode: int) -> None:
     _lib("gemm_tcgen05.cu").gl_gemm_tcgen05_set_split(c_int(mode))
 
 
+def _second_product(g: _GemmArgs, a, w, second) -> None:
+    """Fill in the operands of a second product summed into the same output."""
+    a2, w2, bias2 = second
+    _need(a2, "a2", torch.bfloat16)
+    _need(w2, "w2", torch.bfloat16)
+    if a2.shape[0] != a.shape[0] or w2.shape[0] != w.shape[0] or a2.shape[1] != w2.shape[1] or a2.shape[1] % 8:
+        raise KernelError(f"second product [{tuple(a2.shape)}] x [{tuple(w2.shape)}] does not fit the first")
+    if bias2 is not None:
+        _need(bias2, "bias2", torch.float32, (w.shape[0],))
+    g.a2, g.w2, g.bias2, g.K2 = a2.data_ptr(), w2.data_ptr(), _addr(bias2), a2.shape[1]
+
+
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
                 add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
-                split_k: int = 0) -> torch.Tensor:
-    """The weight-streaming product for up to 64 rows of bfloat16 activations (K a multiple of 8)."""
+                split_k: int = 0, second=None) -> torch.Tensor:
+    """The weight-streaming product for up to 64 rows of bfloat16 activations (K a multiple of 8).
+    ``second`` = (a2, w2, bias2) sums another product into the same output (K a multiple of 64 then)."""
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     if out is None:
@@ -448,6 +461,10 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[0] > SKINNY_MAX_ROWS or a.shape[1] % 8:
         raise KernelError(f"gemm_skinny takes up to {SKINNY_MAX_ROWS} rows and K a multiple of 8")
+    if second is not None:
+        if a.shape[1] % 64:
+            raise KernelError("gemm_skinny takes a second product only behind a K that is a multiple of 64")
+        _second_product(g, a, w, second)
     fn = _lib("gemm_skinny.cu").gl_gemm_skinny
     _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_skinny")
     return out
@@ -469,14 +486,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     if a.shape[1] % 8:
         raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
     if second is not None:
-        a2, w2, bias2 = second
-        _need(a2, "a2", torch.bfloat16)
-        _need(w2, "w2", torch.bfloat16)
-        if a2.shape[0] != a.shape[0] or w2.shape[0] != w.shape[0] or a2.shape[1] != w2.shape[1] or a2.shape[1] % 8:
-            raise KernelError(f"second product [{tuple(a2.shape)}] x [{tuple(w2.shape)}] does not fit the first")
-        if bias2 is not None:
-            _need(bias2, "bias2", torch.float32, (w.shape[0],))
-        g.a2, g.w2, g.bias2, g.K2 = a2.data_ptr(), w2.data_ptr(), _addr(bias2), a2.shape[1]
+        _second_product(g, a, w, second)
     if tile_n not in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
         raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256; "
                           "1000 more for tiles of 256 rows (160, 192, 256)")
@@ -500,12 +510,17 @@ def linear_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
                 a2: torch.Tensor, w2: torch.Tensor, bias2: Optional[torch.Tensor],
                 add0: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = a·wᵀ + bias + a2·w2ᵀ + bias2 + add0: the last products of two branches that are added
-    to the same rows.  With many bfloat16 rows both run as one tensor-core product over the joined K
-    (one pass over the output instead of two); otherwise one after the other, each adding onto out."""
-    if (USE_TCGEN05 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a2.dtype == torch.bfloat16
-            and w2.dtype == torch.bfloat16 and a.shape[0] > SKINNY_MAX_ROWS and a.shape[1] % 8 == 0
-            and a2.shape[1] % 8 == 0):
-        return gemm_tcgen05(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
+    to the same rows.  In bfloat16 both run as one product over the joined K (one kernel, one pass
+    over the output); otherwise one after the other, each adding onto out."""
+    if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a2.dtype == torch.bfloat16
+            and w2.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a2.shape[1] % 8 == 0):
+        if a.shape[0] <= SKINNY_MAX_ROWS:
+            if a.shape[1] % 64 == 0:
+                return gemm_skinny(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
+            if a2.shape[1] % 64 == 0:                  # the product whose K fills whole stages goes first
+                return gemm_skinny(a2, w2, bias2, None, add0, None, torch.float32, out, second=(a, w, bias))
+        elif USE_TCGEN05:
+            return gemm_tcgen05(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
     out = linear(a, w, bias, add0=add0, out_dtype=torch.float32, out=out)
     return linear(a2, w2, bias2, add0=out, out=out)
 

@@ -50,11 +50,25 @@ class ParallelBlock(_AssembledBlock):
     def forward(self, x, ctx, cache):
         xn = self.norm.forward(x, ctx.act_dtype)
         side = getattr(ctx, "side_stream", None)
-        if side is None and self.ffn.until_last is not None and self.mixer.until_last is not None:
-            # the branches' last products end on the same rows and columns: one product over the joined
-            # K where the kernels can (one pass over the residual stream), else one after the other
-            h, w2, b2 = self.ffn.until_last(xn, ctx)
-            o, wo, bo = self.mixer.until_last(xn, ctx, cache)
+        if self.ffn.until_last is not None and self.mixer.until_last is not None:
+            # The branches' last products end on the same rows and columns: they run as one product
+            # over the joined K where the kernels can (one kernel, one pass over the residual stream),
+            # else one after the other.  What comes before them runs on two streams in decode steps:
+            # with few tokens every kernel is a stream of weights, and the feed-forward's first product
+            # keeps memory busy while the mixer's small kernels start and finish.
+            if side is None:
+                h, w2, b2 = self.ffn.until_last(xn, ctx)
+                o, wo, bo = self.mixer.until_last(xn, ctx, cache)
+            else:
+                main = torch.cuda.current_stream()
+                fork, join = torch.cuda.Event(), torch.cuda.Event()
+                fork.record(main)
+                side.wait_event(fork)
+                with torch.cuda.stream(side):
+                    h, w2, b2 = self.ffn.until_last(xn, ctx)
+                    join.record(side)
+                o, wo, bo = self.mixer.until_last(xn, ctx, cache)
+                main.wait_event(join)
             ops.linear_pair(h, w2, b2, o, wo, bo, add0=x, out=x)
             return x
         if side is None or not self.mixer.deferred_add:

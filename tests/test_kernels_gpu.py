@@ -200,6 +200,25 @@ def test_gemm_tcgen05_one_weight_stands_out():
             assert torch.equal(got, want), (m, k, tile)
 
 
+@pytest.mark.parametrize("M,N,K1,K2", [(8, 200, 64, 160), (1, 2560, 2560, 10240), (64, 520, 192, 1096), (17, 77, 128, 8)])
+def test_gemm_skinny_two_products_one_output(M, N, K1, K2):
+    o = ops()
+    a1, w1 = rnd(M, K1, dtype=torch.bfloat16), rnd(N, K1, dtype=torch.bfloat16, scale=0.05, seed=1)
+    a2, w2 = rnd(M, K2, dtype=torch.bfloat16, seed=5), rnd(N, K2, dtype=torch.bfloat16, scale=0.05, seed=6)
+    b1, b2, x0 = rnd(N, seed=2), rnd(N, seed=7), rnd(M, N, seed=3)
+    want = ref_linear(a1, w1, b1, None, x0, None) + ref_linear(a2, w2, b2, None, None, None)
+    for split in (0, 1, 2, 4, 8):
+        x = x0.clone()
+        o.gemm_skinny(a1, w1, b1, None, x, out=x, split_k=split, second=(a2, w2, b2))
+        torch.cuda.synchronize()
+        assert o.wait_failures()["gemm_skinny.cu"] == 0, "a bounded wait ran out"
+        err = (x.double() - want).abs().max().item()
+        assert err <= 3e-5 * max(1.0, want.abs().max().item()), (split, err)
+    x = x0.clone()
+    o.linear_pair(a2, w2, b2, a1, w1, b1, add0=x, out=x)           # K2 first: the dispatcher puts whole stages first
+    assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
+
+
 def test_gemm_skinny_one_weight_stands_out():
     """A single large weight far along K must reach exactly one output."""
     o = ops()
