@@ -87,8 +87,8 @@ struct AttnArgs {
 
 struct AttnMaps { CUtensorMap q[4], k[4], v; };
 
-// Measurement only (AT_PROFILE): clocks one row thread and the issuing thread of block 0 spend in
-// each phase of a step.
+// Measurement only (AT_PROFILE): clocks the first row thread of block 0 spends in each phase of a page
+// (waiting for scores, loading them, maximum, rescaling, exp and store, hand-over).
 #ifdef AT_PROFILE
 __device__ long long at_prof[32];
 #define AT_PROF_BEGIN(on) const bool prof_on = (on); long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
