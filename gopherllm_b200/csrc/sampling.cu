@@ -125,30 +125,63 @@ sample_kernel(SampleArgs a) {
 
     // 1. copy, with every non-finite value as -inf; then the repeat penalty, once per
     //    occurrence in the window and in window order (sampling.go:136-153)
-    for (int i = tid; i < V; i += SM_THREADS) {
-        const float v = src[i];
-        w[i] = finite_bits(v) ? v : -INFINITY;
-    }
-    __syncthreads();
-    if (tid == 0 && a.repeat_penalty != 1.0f) {
-        const int n = min(a.recent_n[row], SM_WINDOW);
-        const int* rc = a.recent + (size_t)row * SM_WINDOW;
-        for (int k = 0; k < n; ++k) {
-            const int t = rc[k];
-            if (t < 0 || t >= V) continue;
-            const float v = w[t];
-            if (!finite_bits(v)) w[t] = -INFINITY;
-            else if (v > 0.f) w[t] = v / a.repeat_penalty;
-            else w[t] = v * a.repeat_penalty;
-        }
-    }
-    __syncthreads();
-
     // 2. the row's maximum, lowest index first (sampling.go:399-418)
     float bv = -INFINITY; int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += SM_THREADS) {
-        const float v = w[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    const bool vec4 = (V & 3) == 0 && (((uintptr_t)src | (uintptr_t)w) & 15) == 0;
+    if ((a.temperature < 1e-6f || a.top_k == 1) && a.repeat_penalty == 1.0f) {
+        // greedy without a penalty needs only the maximum: one pass over the logits, no copy
+        if (vec4) {
+            const float4* s4 = (const float4*)src;
+            for (int i = tid; i < (V >> 2); i += SM_THREADS) {
+                const float4 q = s4[i];
+                const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float v = finite_bits(e[k]) ? e[k] : -INFINITY;
+                    if (v > bv) { bv = v; bi = 4 * i + k; }        // indices only grow inside a thread
+                }
+            }
+        } else {
+            for (int i = tid; i < V; i += SM_THREADS) {
+                const float v0 = src[i];
+                const float v = finite_bits(v0) ? v0 : -INFINITY;
+                if (v > bv) { bv = v; bi = i; }
+            }
+        }
+    } else {
+        if (vec4) {
+            const float4* s4 = (const float4*)src;
+            float4* w4 = (float4*)w;
+            for (int i = tid; i < (V >> 2); i += SM_THREADS) {
+                float4 q = s4[i];
+                q.x = finite_bits(q.x) ? q.x : -INFINITY; q.y = finite_bits(q.y) ? q.y : -INFINITY;
+                q.z = finite_bits(q.z) ? q.z : -INFINITY; q.w = finite_bits(q.w) ? q.w : -INFINITY;
+                w4[i] = q;
+            }
+        } else {
+            for (int i = tid; i < V; i += SM_THREADS) {
+                const float v = src[i];
+                w[i] = finite_bits(v) ? v : -INFINITY;
+            }
+        }
+        __syncthreads();
+        if (tid == 0 && a.repeat_penalty != 1.0f) {
+            const int n = min(a.recent_n[row], SM_WINDOW);
+            const int* rc = a.recent + (size_t)row * SM_WINDOW;
+            for (int k = 0; k < n; ++k) {
+                const int t = rc[k];
+                if (t < 0 || t >= V) continue;
+                const float v = w[t];
+                if (!finite_bits(v)) w[t] = -INFINITY;
+                else if (v > 0.f) w[t] = v / a.repeat_penalty;
+                else w[t] = v * a.repeat_penalty;
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < V; i += SM_THREADS) {
+            const float v = w[i];
+            if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
     }
     block_argmax(bv, bi, s_f, s_i, &s_best, &s_besti);
     const float vmax = s_best;
