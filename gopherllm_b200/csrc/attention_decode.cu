@@ -47,6 +47,56 @@ struct DecodeArgs {
     int B, nH, nKV, max_pages, window, splits;
 };
 
+// Queries, and the new token's key and value, straight from the projection's output: with qkv set the
+// kernel rotates and scales the queries itself as it loads them (DecodeArgs.q is not read), and the block
+// that owns the sequence's last page rotates the new key, writes it and the new value into the cache
+// (write_kv) and into its own copy of the page.  Split-half pairing of the rotary dims, bfloat16, no
+// per-head norm: what the separate kernel does for those cases, with the same arithmetic.  A record of
+// its own, so that DecodeArgs stays what callers of the other entry points compiled against.
+struct DecodeQkv {
+    const __nv_bfloat16* qkv;    // [B, (nH + 2 nKV) * hd] or null
+    const float* cosv;           // [B, half] or null (no rotation)
+    const float* sinv;
+    int half;                    // pairs of rotary dims (a multiple of 8)
+    int write_kv;
+    float q_scale;
+};
+
+// One 16-byte chunk (8 dims starting at dim 8 c) of a head of the projection's output for token b,
+// rotated if it lies in the rotary part and scaled: the arithmetic of qkv_cache_bf16_kernel.
+__device__ __forceinline__ uint4 ad_rotated_chunk(const __nv_bfloat16* head, int c, int half, const float* cs, const float* sn, float sc) {
+    const uint4 raw = *(const uint4*)(head + c * 8);
+    float v[8];
+    {
+        const __nv_bfloat162* p2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+    }
+    const int hc = half >> 3;
+    if (cs && c < 2 * hc) {
+        const bool low = c < hc;
+        const uint4 praw = *(const uint4*)(head + (low ? c + hc : c - hc) * 8);
+        const __nv_bfloat162* q2 = (const __nv_bfloat162*)&praw;
+        const float* csp = cs + (low ? c : c - hc) * 8;
+        const float* snp = sn + (low ? c : c - hc) * 8;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(q2[e]);
+            const float pw[2] = {f.x, f.y};
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const float co = csp[2 * e + k], si = snp[2 * e + k];
+                v[2 * e + k] = low ? v[2 * e + k] * co - pw[k] * si : pw[k] * si + v[2 * e + k] * co;
+            }
+        }
+    }
+    uint4 out;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0] * sc, v[1] * sc), p1 = __floats2bfloat162_rn(v[2] * sc, v[3] * sc);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4] * sc, v[5] * sc), p3 = __floats2bfloat162_rn(v[6] * sc, v[7] * sc);
+    out.x = *(unsigned*)&p0; out.y = *(unsigned*)&p1; out.z = *(unsigned*)&p2; out.w = *(unsigned*)&p3;
+    return out;
+}
+
 __device__ __forceinline__ unsigned ad_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ad_cp16(unsigned dst, const void* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
@@ -85,7 +135,7 @@ __device__ __forceinline__ void ad_load_page(unsigned dst, const __nv_bfloat16* 
 // CLUSTER: the splits of one (sequence, key/value head) are the blocks of a cluster
 template <bool CLUSTER>
 __global__ void __launch_bounds__(AD_THREADS)
-attn_decode_kernel(DecodeArgs a) {
+attn_decode_kernel(DecodeArgs a, DecodeQkv x) {
     extern __shared__ __align__(16) unsigned char smem[];
     // stage s: keys at 2 s AD_TILE, values one tile further; then per-warp scratch
     const unsigned sbase = ad_smem(smem);
@@ -110,7 +160,26 @@ attn_decode_kernel(DecodeArgs a) {
 
     // the queries as the 8-column operand: column = head within the group, rows = head dims
     unsigned qb[AD_KS][2];
-    {
+    const size_t qkv_row = (size_t)(a.nH + 2 * a.nKV) * AD_HD;
+    if (x.qkv) {
+        // rotated and scaled here: the group's query heads through this block's corner of shared memory
+        __nv_bfloat16* qs = (__nv_bfloat16*)mrg;                       // [G][hd], free until the merge
+        const float* cs = x.cosv ? x.cosv + (size_t)b * x.half : nullptr;
+        const float* sn = x.sinv ? x.sinv + (size_t)b * x.half : nullptr;
+        for (int i = tid; i < G * AD_CHUNKS; i += AD_THREADS) {
+            const int hq = i / AD_CHUNKS, c = i - hq * AD_CHUNKS;
+            const __nv_bfloat16* head = x.qkv + (size_t)b * qkv_row + ((size_t)g * G + hq) * AD_HD;
+            *(uint4*)(qs + hq * AD_HD + c * 8) = ad_rotated_chunk(head, c, x.half, cs, sn, x.q_scale);
+        }
+        __syncthreads();
+        const __nv_bfloat16* qh = qs + grp * AD_HD;
+#pragma unroll
+        for (int kk = 0; kk < AD_KS; ++kk) {
+            qb[kk][0] = grp < G ? *(const unsigned*)(qh + kk * 16 + 2 * t) : 0u;
+            qb[kk][1] = grp < G ? *(const unsigned*)(qh + kk * 16 + 8 + 2 * t) : 0u;
+        }
+        __syncthreads();
+    } else {
         const __nv_bfloat16* qh = a.q + ((size_t)b * a.nH + (size_t)g * G + grp) * AD_HD;
 #pragma unroll
         for (int kk = 0; kk < AD_KS; ++kk) {
@@ -150,6 +219,21 @@ attn_decode_kernel(DecodeArgs a) {
             ad_commit();
         }
         const unsigned Ks = sbase + 2 * st * AD_TILE, Vs = Ks + AD_TILE;
+        if (x.qkv && x.write_kv && p == pos / GL_PAGE) {
+            // the new token's key (rotated) and value: into the cache for the steps to come, and over
+            // the row of this block's copy of the page that the copy from the cache brought stale
+            if (tid < 2 * AD_CHUNKS) {
+                const int c = tid % AD_CHUNKS, is_v = tid / AD_CHUNKS, r = pos % GL_PAGE;
+                const __nv_bfloat16* head = x.qkv + (size_t)b * qkv_row + ((size_t)a.nH + (size_t)is_v * a.nKV + g) * AD_HD;
+                const float* cs = (!is_v && x.cosv) ? x.cosv + (size_t)b * x.half : nullptr;
+                const float* sn = (!is_v && x.sinv) ? x.sinv + (size_t)b * x.half : nullptr;
+                const uint4 val = ad_rotated_chunk(head, c, is_v ? 0 : x.half, cs, sn, 1.0f);
+                *(uint4*)(smem + (2 * st + is_v) * AD_TILE + r * AD_ROW + c * 16) = val;
+                __nv_bfloat16* cache = (__nv_bfloat16*)(is_v ? a.v_cache : a.k_cache);
+                *(uint4*)(cache + (size_t)pg[p] * page_stride + head_off + (size_t)r * AD_HD + c * 8) = val;
+            }
+            __syncthreads();
+        }
         const int j0 = p * GL_PAGE + warp * 16;          // this warp's first key
         if (j0 > pos) continue;                          // all of this warp's keys lie past the sequence
         // scores: [16 keys] x [8 heads]
@@ -310,7 +394,7 @@ static size_t decode_smem(int G) {
     return 2 * AD_STAGES * (size_t)AD_TILE + 4 * 8 * 16 * 2 + sizeof(float) * (64 + 5 * (size_t)AD_HD * G + 2 * G);
 }
 
-static int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
+static int launch_decode(const DecodeArgs& a, const DecodeQkv& x, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = decode_smem(a.nH / a.nKV);
     if (!configured) {
@@ -323,8 +407,8 @@ static int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     }
     const dim3 grid(a.splits, a.nKV, a.B);
     if (a.splits > 1 && a.splits <= 8 && !a.part_o)
-        return gl_launch(attn_decode_kernel<true>, grid, dim3(AD_THREADS), smem, stream, a.splits, a);
-    return gl_launch(attn_decode_kernel<false>, grid, dim3(AD_THREADS), smem, stream, 1, a);
+        return gl_launch(attn_decode_kernel<true>, grid, dim3(AD_THREADS), smem, stream, a.splits, a, x);
+    return gl_launch(attn_decode_kernel<false>, grid, dim3(AD_THREADS), smem, stream, 1, a, x);
 }
 
 GL_API int gl_attention_decode_head_dim() { return AD_HD; }
@@ -334,14 +418,28 @@ GL_API long long gl_attention_decode_scratch(int B, int nH, int splits) {
     return splits > 1 ? (long long)B * nH * splits * (AD_HD + 2) : 0;
 }
 
+static int decode_checked(const DecodeArgs& a, const DecodeQkv& x, cudaStream_t stream);
+
 GL_API int gl_attention_decode(const DecodeArgs* args, cudaStream_t stream) {
-    const DecodeArgs& a = *args;
+    const DecodeQkv none = {nullptr, nullptr, nullptr, 0, 0, 1.0f};
+    return decode_checked(*args, none, stream);
+}
+
+// the same with the queries and the new key and value taken from the projection's output
+GL_API int gl_attention_decode_qkv(const DecodeArgs* args, const DecodeQkv* extra, cudaStream_t stream) {
+    const DecodeQkv& x = *extra;
+    if (!x.qkv || x.half < 0 || x.half % 8 || 2 * x.half > AD_HD || (x.half > 0 && (!x.cosv || !x.sinv))) return GL_ERR_SHAPE;
+    if (((uintptr_t)x.qkv | (uintptr_t)args->k_cache | (uintptr_t)args->v_cache) & 15) return GL_ERR_ALIGN;
+    return decode_checked(*args, x, stream);
+}
+
+static int decode_checked(const DecodeArgs& a, const DecodeQkv& x, cudaStream_t stream) {
     if (a.B <= 0) return GL_OK;
     if (a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV || a.nH / a.nKV > AD_MAXG) return GL_ERR_SHAPE;
     if (a.splits < 1 || a.B > 65535 || a.nKV > 65535) return GL_ERR_SHAPE;
     if (a.splits > 8 && (!a.part_o || !a.part_ml)) return GL_ERR_SHAPE;     // more than a cluster holds: scratch
     if ((a.part_o == nullptr) != (a.part_ml == nullptr)) return GL_ERR_SHAPE;
-    const int rc = launch_decode(a, stream);
+    const int rc = launch_decode(a, x, stream);
     if (rc != GL_OK) return rc;
     if (a.splits > 1 && a.part_o) {
         return gl_launch(attn_decode_merge_kernel, dim3(a.nH, a.B), dim3(AD_HD >= 128 ? 128 : 64), 0, stream, 1, a);

@@ -293,6 +293,11 @@ class _DecodeArgs(Structure):
                 ("splits", c_int)]
 
 
+class _DecodeQkv(Structure):
+    _fields_ = [("qkv", c_void_p), ("cosv", c_void_p), ("sinv", c_void_p), ("half", c_int), ("write_kv", c_int),
+                ("q_scale", c_float)]
+
+
 DECODE_MAX_GROUP = 8      # query heads per key/value head the decode kernel takes
 _SM_COUNT = {}
 
@@ -321,16 +326,39 @@ def decode_splits(batch: int, num_kv_heads: int, max_len: int, device, head_dim:
     return max(1, min(slots // max(1, batch * num_kv_heads), pages, 8))
 
 
+def decode_takes_qkv(act_dtype, cache_dtype, head_dim: int, rotary_half: int, interleaved: bool,
+                     head_norm: bool) -> bool:
+    """Whether decode attention can take the projection's output itself (rotating and scaling the
+    queries, rotating and storing the new key and value) instead of a pass of qkv_to_cache first."""
+    return (act_dtype == torch.bfloat16 and cache_dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
+            and rotary_half % 8 == 0 and not interleaved and not head_norm)
+
+
 def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, num_kv_heads: int,
                      head_dim: int, splits: int, window: int = 0,
-                     scratch: Optional[torch.Tensor] = None) -> None:
+                     scratch: Optional[torch.Tensor] = None, qkv: Optional[torch.Tensor] = None,
+                     cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                     q_scale: float = 1.0, write_kv: bool = True) -> None:
     """One query per sequence (row b of q is sequence b) over the bfloat16 cache.
     Up to 8 splits merge inside a thread-block cluster and need no scratch.  More splits, or
     ``scratch`` given (float32, at least B*nH*splits*(hd+2) elements), write partial results
-    to scratch (allocated here when needed and not given) for a second kernel to merge."""
-    B = q.shape[0]
-    _need(q, "q", torch.bfloat16, (B, num_heads * head_dim))
-    _need(out, "out", torch.bfloat16, q.shape)
+    to scratch (allocated here when needed and not given) for a second kernel to merge.
+    With ``qkv`` ([B, (heads + 2 kv heads) * head size], the projection's output; q is None then)
+    the kernel rotates (cos, sin: [B, half] float32, split-half pairing) and scales the queries itself,
+    and stores the new token's rotated key and its value in the cache (write_kv) before it reads them."""
+    B = out.shape[0]
+    if qkv is not None:
+        _need(qkv, "qkv", torch.bfloat16, (B, (num_heads + 2 * num_kv_heads) * head_dim))
+        half = 0
+        if cos is not None:
+            _need(cos, "cos", torch.float32)
+            _need(sin, "sin", torch.float32, cos.shape)
+            half = cos.shape[1]
+            if cos.shape[0] != B or half % 8 or 2 * half > head_dim:
+                raise KernelError(f"rotary tables {tuple(cos.shape)} do not fit {B} tokens of head size {head_dim}")
+    else:
+        _need(q, "q", torch.bfloat16, (B, num_heads * head_dim))
+    _need(out, "out", torch.bfloat16, (B, num_heads * head_dim))
     _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
     if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
@@ -348,15 +376,21 @@ def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, n
     if splits > 8 or (splits > 1 and scratch is not None):
         n_o, n_ml = B * num_heads * splits * head_dim, B * num_heads * splits * 2
         if scratch is None:
-            scratch = torch.empty(n_o + n_ml, dtype=torch.float32, device=q.device)
+            scratch = torch.empty(n_o + n_ml, dtype=torch.float32, device=out.device)
         _need(scratch, "scratch", torch.float32)
         if scratch.numel() < n_o + n_ml:
             raise KernelError("decode attention scratch is too small")
         part_o, part_ml = scratch.data_ptr(), scratch.data_ptr() + 4 * n_o
-    a = _DecodeArgs(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+    a = _DecodeArgs(_addr(q), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                     seq_ctx.data_ptr(), pages.data_ptr(), part_o, part_ml,
                     B, num_heads, num_kv_heads, pages.shape[-1], window, splits)
-    _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode", 2 if part_o is not None else 1)
+    launches = 2 if part_o is not None else 1
+    if qkv is None:
+        _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode", launches)
+    else:
+        x = _DecodeQkv(qkv.data_ptr(), _addr(cos), _addr(sin), cos.shape[1] if cos is not None else 0,
+                       int(bool(write_kv)), float(q_scale))
+        _check(lib.gl_attention_decode_qkv(byref(a), byref(x), _stream()), "attention_decode", launches)
 
 
 def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads: int,

@@ -81,10 +81,22 @@ class Attention(Mixer):
         s = self.spec
         T = xn.shape[0]
         qkv = ops.linear(xn, self.w_qkv, self.b_qkv, out_dtype=ctx.act_dtype)
-        q = torch.empty((T, s.num_heads * s.head_dim), dtype=ctx.act_dtype, device=xn.device)
         tables = self.position.tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
         pages = ctx.pages[cache.group]
+        group = s.num_heads // s.num_kv_heads
+        if (ctx.is_decode and group <= ops.DECODE_MAX_GROUP
+                and ops.decode_takes_qkv(qkv.dtype, cache.k.dtype, s.head_dim, 0 if cos is None else cos.shape[1],
+                                         s.position.interleaved, self.q_norm is not None)):
+            # one token a sequence: attention reads the projection's output itself (rotation, query scale
+            # and the cache write happen inside it), one kernel less between two products
+            o = torch.empty((T, s.num_heads * s.head_dim), dtype=ctx.act_dtype, device=xn.device)
+            splits = ops.decode_splits(ctx.n_seqs, s.num_kv_heads, ctx.max_len, xn.device, s.head_dim, group)
+            ops.attention_decode(None, o, cache.k, cache.v, ctx.seq_ctx, pages, s.num_heads, s.num_kv_heads,
+                                 s.head_dim, splits, s.window, qkv=qkv, cos=cos, sin=sin, q_scale=s.q_scale,
+                                 write_kv=cache.writes)
+            return o, self.w_out, self.b_out
+        q = torch.empty((T, s.num_heads * s.head_dim), dtype=ctx.act_dtype, device=xn.device)
         qn = kn = None
         eps, rms = 0.0, False
         if self.q_norm is not None:

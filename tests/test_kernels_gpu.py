@@ -371,6 +371,44 @@ def test_attention_decode(nH, nKV, hd, window):
             assert (got - ref).abs().max() <= 2 ** -7 * max(1.0, ref.abs().max().item()), (b, splits)
 
 
+@pytest.mark.parametrize("nH,nKV,hd,rot", [(4, 4, 16, 16), (4, 2, 80, 32), (6, 2, 48, 0), (8, 1, 64, 16), (2, 2, 256, 64), (3, 3, 32, 32)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode_from_the_projection(nH, nKV, hd, rot, window):
+    """Decode attention that takes the projection's output (rotating and scaling the queries, storing the
+    new key and value itself) against the separate kernel followed by decode attention: the same output
+    bit for bit and the same cache, at the new positions and everywhere else."""
+    o = ops()
+    ctxs = [0, 63, 64, 700, 1, 333]
+    B, L = len(ctxs), max(ctxs) + 1
+    dtype = torch.bfloat16
+    k = rnd(B, L, nKV, hd, seed=1).to(dtype).float()
+    v = rnd(B, L, nKV, hd, seed=2).to(dtype).float()
+    lens = [c + 1 for c in ctxs]
+    kc0, vc0, table = make_cache(k, v, lens, dtype, seed=3)
+    i32 = lambda x: torch.tensor(np.asarray(x), dtype=torch.int32, device=DEV)
+    qkv = rnd(B, (nH + 2 * nKV) * hd, seed=4).to(dtype)
+    cos = sin = None
+    if rot:
+        from gopherllm_b200.parts.position import rope_inverse_frequencies
+        cos, sin = o.rope_table(i32(ctxs), torch.from_numpy(rope_inverse_frequencies(rot, 10000.0)).to(DEV))
+    scale = 1.0 / math.sqrt(hd)
+    for write_kv in (True, False):
+        for splits in (1, 2, 5, 8, 16):
+            kc_a, vc_a, kc_b, vc_b = kc0.clone(), vc0.clone(), kc0.clone(), vc0.clone()
+            q = torch.empty(B, nH * hd, dtype=dtype, device=DEV)
+            o.qkv_to_cache(qkv, q, kc_a, vc_a, i32(np.arange(B)), i32(ctxs), table, nH, nKV, hd, scale, cos, sin,
+                           write_kv=write_kv)
+            want = torch.empty(B, nH * hd, dtype=dtype, device=DEV)
+            o.attention_decode(q, want, kc_a, vc_a, i32(ctxs), table, nH, nKV, hd, splits, window)
+            got = torch.empty_like(want)
+            o.attention_decode(None, got, kc_b, vc_b, i32(ctxs), table, nH, nKV, hd, splits, window,
+                               qkv=qkv, cos=cos, sin=sin, q_scale=scale, write_kv=write_kv)
+            torch.cuda.synchronize()
+            same = lambda x, y: torch.equal(x.view(torch.int16), y.view(torch.int16))      # unused cells are NaN
+            assert same(kc_a, kc_b) and same(vc_a, vc_b), (write_kv, splits)
+            assert torch.equal(got, want), (write_kv, splits, (got.float() - want.float()).abs().max().item())
+
+
 @pytest.mark.parametrize("kernel", ["generic32", "generic16", "decode", "prefill", "prefill_tc"])
 def test_attention_far_key_and_window_edge(kernel):
     """One key among hundreds carries the whole weight: its value must come back.  With a
