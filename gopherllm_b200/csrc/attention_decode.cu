@@ -158,6 +158,17 @@ attn_decode_kernel(DecodeArgs a, DecodeQkv x) {
     const size_t head_off = (size_t)g * GL_PAGE * AD_HD;
     const size_t page_stride = (size_t)a.nKV * GL_PAGE * AD_HD;
 
+    // the first pages are under way before anything else is fetched
+#pragma unroll
+    for (int s = 0; s < AD_STAGES - 1; ++s) {
+        const int p = p_begin + s;
+        if (p < p_end) {
+            const int nv = min(GL_PAGE, pos + 1 - p * GL_PAGE);
+            ad_load_page(sbase + 2 * s * AD_TILE, a.k_cache + (size_t)pg[p] * page_stride + head_off, nv);
+            ad_load_page(sbase + (2 * s + 1) * AD_TILE, a.v_cache + (size_t)pg[p] * page_stride + head_off, nv);
+        }
+        ad_commit();
+    }
     // the queries as the 8-column operand: column = head within the group, rows = head dims
     unsigned qb[AD_KS][2];
     const size_t qkv_row = (size_t)(a.nH + 2 * a.nKV) * AD_HD;
@@ -195,16 +206,6 @@ attn_decode_kernel(DecodeArgs a, DecodeQkv x) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};      // heads 2t, 2t+1; this warp's keys only
     const float LOG2E = 1.4426950408889634f;
 
-#pragma unroll
-    for (int s = 0; s < AD_STAGES - 1; ++s) {
-        const int p = p_begin + s;
-        if (p < p_end) {
-            const int nv = min(GL_PAGE, pos + 1 - p * GL_PAGE);
-            ad_load_page(sbase + 2 * s * AD_TILE, a.k_cache + (size_t)pg[p] * page_stride + head_off, nv);
-            ad_load_page(sbase + (2 * s + 1) * AD_TILE, a.v_cache + (size_t)pg[p] * page_stride + head_off, nv);
-        }
-        ad_commit();
-    }
     for (int p = p_begin; p < p_end; ++p) {
         const int st = (p - p_begin) % AD_STAGES;
         ad_wait<AD_STAGES - 2>();
