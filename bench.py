@@ -182,7 +182,8 @@ def main():
         res = model.generate(prompts, max_tokens=K + W, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
                              stop_tokens=(), seed=5)
         # the W tokens after the prompt are warm-up, as in the device-timed loop: the last K count
-        dec_s = max(r.stats.token_times[-1] - r.stats.token_times[-1 - K] for r in res)
+        dec_s = max(r.stats.token_times[-1] - (r.stats.token_times[-1 - K] if len(r.stats.token_times) > K
+                                                 else r.stats.prefill_time) for r in res)
         e2e_value = B * K / dec_s
         e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.h2d_bytes_last + 4 * B,
                "d2h_bytes_per_step": 4 * B}
