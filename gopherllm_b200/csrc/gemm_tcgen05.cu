@@ -359,7 +359,9 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     const bool uneven = tiles % sms != 0 && (long long)tiles * 100 < (long long)waves * sms * 92;
     // (alone it pays only for a long K: a cut tile costs a second add-reduction of its 32-bit patch)
     const bool can_split = out_mode == 2 && g.act == GL_ACT_NONE && (long long)tiles * k_blocks >= 8LL * sms;
-    const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64));
+    // (with few rows the tiles are far fewer than the SMs: equal shares then whatever the mode, since a
+    // third of the machine would otherwise stream all the weights)
+    const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 2 <= sms);
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
     gemm_tcgen05_kernel<BN, STAGES, TO, MT><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_a2, map_w2, map_out, out_mode, split);
     return gl_check_launch();
@@ -423,8 +425,9 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
         // product): tiles of 256 x 160 when one wave of them covers the output.  Two products of a
         // k-step then share the weight tile (81 instead of 112 bytes from L2 per clock of tensor work);
         // measured 108 against 127 us at 2048 x 2560 x 10240.  Shorter products gain nothing from it.
-        if (out_dtype == GL_F32 && g.add0 == (const float*)g.out && !g.add1 && g.K + (g.a2 ? g.K2 : 0) >= 5120 && g.M > 128 &&
-            ((g.M + 255) / 256) * ((g.N + 159) / 160) <= sms)
+        const int big_tiles = ((g.M + 255) / 256) * ((g.N + 159) / 160);
+        if (out_dtype == GL_F32 && g.add0 == (const float*)g.out && !g.add1 && g.K + (g.a2 ? g.K2 : 0) >= 5120 &&
+            big_tiles <= sms && big_tiles * 10 >= sms * 7)      // (fewer would leave SMs idle, or cut tiles into costly parts)
             bn = 1160;
     }
     if (out_dtype == GL_F32) return dispatch_bn<float>(g, bn, stream);

@@ -54,7 +54,14 @@ def dtype_code(t: torch.dtype) -> int:
     raise KernelError(f"element type {t} is not supported by the kernels (float32 and bfloat16 are)")
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    # (the raw handle straight from the runtime: a step launches a few hundred kernels, and building a
+    # Stream object for each costs more host time than a short kernel runs)
+    if _RAW_STREAM is not None:
+        return c_void_p(_RAW_STREAM(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -78,8 +85,15 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
         raise KernelError(f"{name} must have shape {tuple(shape)}, has {tuple(t.shape)}")
 
 
+_LIBS: dict = {}
+
+
 def _lib(source: str, defines=()):
-    return build.load(source, tuple(defines))
+    key = (source, tuple(defines))
+    lib = _LIBS.get(key)
+    if lib is None:
+        lib = _LIBS[key] = build.load(source, key[1])
+    return lib
 
 
 # ---------------------------------------------------------------------------
