@@ -359,9 +359,9 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     const bool uneven = tiles % sms != 0 && (long long)tiles * 100 < (long long)waves * sms * 92;
     // (alone it pays only for a long K: a cut tile costs a second add-reduction of its 32-bit patch)
     const bool can_split = out_mode == 2 && g.act == GL_ACT_NONE && (long long)tiles * k_blocks >= 8LL * sms;
-    // (with few rows the tiles are far fewer than the SMs: equal shares then whatever the mode, since a
-    // third of the machine would otherwise stream all the weights)
-    const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 2 <= sms);
+    // (with few rows the tiles are fewer than the SMs: equal shares then whatever the mode when under 70 %
+    // of the SMs would have a tile, since part of the machine would otherwise stream all the weights)
+    const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 10 < sms * 7);
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
     gemm_tcgen05_kernel<BN, STAGES, TO, MT><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_a2, map_w2, map_out, out_mode, split);
     return gl_check_launch();
