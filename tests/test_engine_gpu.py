@@ -125,6 +125,42 @@ def test_unequal_batches_one_after_another(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_prompts_in_pieces_of_unequal_sizes(name, dtype):
+    """Prompts fed in several steps of more than one token each, the sequences of a step with different
+    piece sizes and different amounts already cached (pieces that end inside a page, on a page's edge,
+    and of one token among long ones): every position's logits as in the whole sequence."""
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(21)
+    m = model(name, dtype)
+    top = cfg["max_position_embeddings"] - 1
+    lens = [min(top, n) for n in (200, 131, 64)]
+    seqs = [tiny.prompt(rng, n, cfg["vocab_size"]) for n in lens]
+    refs = [plain_logits(name, s) for s in seqs]
+    pieces = [[70, 1, 58, 71], [64, 64, 3], [5, 33, 26]]
+    slots = [m.open_sequence() for _ in seqs]
+    done = [0, 0, 0]
+    for step in range(4):
+        live = [i for i in range(3) if step < len(pieces[i]) and done[i] < lens[i]]
+        if not live:
+            break
+        runs, want = [], []
+        for i in live:
+            n = min(pieces[i][step], lens[i] - done[i])
+            runs.append((slots[i], seqs[i][done[i]:done[i] + n]))
+            want.append(list(range(n)))
+        got = m.step(runs, want).cpu().numpy()
+        o = 0
+        for i, (_, toks) in zip(live, runs):
+            check(got[o:o + len(toks)], refs[i][done[i]:done[i] + len(toks)], dtype, f"{name} step {step} sequence {i}")
+            o += len(toks)
+            done[i] += len(toks)
+    for s in slots:
+        m.close_sequence(s)
+    m.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_long_decoding(dtype):
     """A short prompt, then decoding up to the model's last position."""
     name = "B"
