@@ -165,6 +165,8 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
     __syncthreads();
     tc_fence_after();
     const unsigned tmem = tmem_slot;
+    gl_grid_launch_dependents();                          // launched programmatically: everything read or written
+    gl_grid_wait();                                       // comes after the kernel before
     // tile t: score buffers at columns 256 t and 256 t + 64 (the weights of a page overwrite the first
     // 32 columns of its scores, two a column), output at 256 t + 128
 
@@ -458,6 +460,6 @@ GL_API int gl_attention_prefill_tc(const AttnArgs* args, int n_tokens, int n_pag
     }
     const long long blocks = (long long)((a.max_qlen + 2 * AT_BM - 1) / (2 * AT_BM)) * a.nH * a.B;
     if (blocks > 0x7fffffffLL) return GL_ERR_SHAPE;
-    attn_prefill_tc_kernel<<<(unsigned)blocks, AT_THREADS, smem, stream>>>(a, maps);
-    return gl_check_launch();
+    if (gl_launch(attn_prefill_tc_kernel, dim3((unsigned)blocks), dim3(AT_THREADS), smem, stream, 1, a, maps) != 0) return GL_ERR_LAUNCH;
+    return GL_OK;
 }

@@ -121,6 +121,9 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = tmem_base_slot;
+    // launched programmatically: set up while the kernel before still runs, read and write after it
+    gl_grid_launch_dependents();
+    gl_grid_wait();
 
     if (warp == 0) {
         // ---- TMA producer -------------------------------------------------
@@ -363,8 +366,10 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     // of the SMs would have a tile, since part of the machine would otherwise stream all the weights)
     const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 10 < sms * 7);
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
-    gemm_tcgen05_kernel<BN, STAGES, TO, MT><<<grid, TG_THREADS, smem, stream>>>(ga, map_a, map_w, map_a2, map_w2, map_out, out_mode, split);
-    return gl_check_launch();
+    if (gl_launch(gemm_tcgen05_kernel<BN, STAGES, TO, MT>, dim3(grid), dim3(TG_THREADS), smem, stream, 1, ga, map_a, map_w, map_a2, map_w2,
+                  map_out, out_mode, split) != 0)
+        return GL_ERR_LAUNCH;
+    return GL_OK;
 }
 
 template <typename TO>
