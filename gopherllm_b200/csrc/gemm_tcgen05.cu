@@ -17,6 +17,8 @@
 //
 // Every wait on an mbarrier is bounded; if one runs out the block records it,
 // leaves its loops, frees its tensor memory and returns.
+#include <type_traits>
+
 #include "common.cuh"
 #include "tma.cuh"
 #include "tcgen05.cuh"
@@ -40,6 +42,13 @@ struct GemmArgs {
     const void* w2;       // [N, K2] bf16
     const float* bias2;   // [N] or null
     int K2;
+    // a second set of columns from the same rows (outB = actB(a wB^T + biasB)): two branches that start
+    // from the same input run as one grid, whose tiles fill the SMs' waves together.  Only with tile
+    // stores (no tensors to add), without a second product and without cut tiles.
+    const void* wB;       // [NB, K] bf16 or null
+    const float* biasB;   // [NB] or null
+    void* outB;           // [M, NB], the type of out
+    int NB, actB;
 };
 
 // The work of one block: whole output tiles taken round-robin, or (split) an equal share of all
@@ -85,7 +94,8 @@ template <int BN, int STAGES, typename TO, int MT>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_w2,
-                    const __grid_constant__ CUtensorMap map_out, int out_mode, int split) {
+                    const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_wB,
+                    const __grid_constant__ CUtensorMap map_outB, int out_mode, int split) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int A_BYTES = MT * TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
     constexpr int NBUF = 2 * MT * BN <= 512 ? 2 : 1;                                      // accumulator sets
@@ -102,7 +112,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     const unsigned bar_tempty = bar_tfull + 16;               // [2] accumulator drained
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (g.M + MT * TG_BM - 1) / (MT * TG_BM), tiles_n = (g.N + BN - 1) / BN;
-    const int n_tiles = tiles_m * tiles_n;
+    const int n_tiles = tiles_m * (tiles_n + (g.wB ? (g.NB + BN - 1) / BN : 0));     // the second set's tiles follow the first's
     const int k1_blocks = (g.K + TG_BK - 1) / TG_BK;                   // k-blocks of the first product
     const int k_blocks = k1_blocks + (g.a2 ? (g.K2 + TG_BK - 1) / TG_BK : 0);
 
@@ -131,7 +141,8 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             int it = 0, tile, kb0, kb1;
             TgWork work(n_tiles, k_blocks, split);
             while (!failed && work.next(tile, kb0, kb1)) {
-                const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m) * BN;
+                const bool fork = tile / tiles_m >= tiles_n;
+                const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m - (fork ? tiles_n : 0)) * BN;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1)) { failed = 1; break; }
@@ -139,7 +150,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     mbar_expect_tx(bar_full + 8 * s, STAGE);
                     const bool second = kb >= k1_blocks;
                     const CUtensorMap* ma = second ? &map_a2 : &map_a;
-                    const CUtensorMap* mw = second ? &map_w2 : &map_w;
+                    const CUtensorMap* mw = fork ? &map_wB : (second ? &map_w2 : &map_w);
                     const int k0 = (second ? kb - k1_blocks : kb) * TG_BK;
 #pragma unroll
                     for (int i = 0; i < MT; ++i)
@@ -195,13 +206,17 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         TgWork work(n_tiles, k_blocks, split);
         for (; work.next(tile, kb0, kb1); ++local) {
             const int buf = local % NBUF, use = local / NBUF;
-            const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m) * BN;
+            const bool fork = tile / tiles_m >= tiles_n;
+            const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m - (fork ? tiles_n : 0)) * BN;
+            const int N = fork ? g.NB : g.N, act = fork ? g.actB : g.act;
+            const float* bias = fork ? g.biasB : g.bias;
+            const CUtensorMap* mo = fork ? &map_outB : &map_out;
             // before the accumulator is ready: this tile's bias into shared memory
             __syncwarp();
             for (int j = lane; j < BN; j += 32) {
                 float bv = 0.f;
-                if (kb0 == 0 && n0 + j < g.N) {
-                    if (g.bias) bv = g.bias[n0 + j];
+                if (kb0 == 0 && n0 + j < N) {
+                    if (bias) bv = bias[n0 + j];
                     if (g.bias2) bv += g.bias2[n0 + j];
                 }
                 bias_s[j] = bv;
@@ -210,6 +225,10 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { failed = 1; break; }
             tc_fence_after();
+            // The activation is a constant inside the loops (one copy of them per kind): a tile's kind is
+            // known only at run time, and a choice per element would put a chain of branches into every value.
+            auto store_tile = [&](auto act_c) {
+            constexpr int ACT = decltype(act_c)::value;
 #pragma unroll 1
             for (int sub = 0; sub < MT; ++sub) {
             const int mrow0 = m0 + sub * TG_BM + quarter * 32;
@@ -229,16 +248,16 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     for (int q = 0; q < 8; ++q) {                        // 16-byte chunks, swizzled as TMA expects
                         uint4 pk;
                         if (CW == 32) {
-                            pk.x = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 0]) + bias_s[c + 4 * q + 0], g.act));
-                            pk.y = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 1]) + bias_s[c + 4 * q + 1], g.act));
-                            pk.z = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 2]) + bias_s[c + 4 * q + 2], g.act));
-                            pk.w = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 3]) + bias_s[c + 4 * q + 3], g.act));
+                            pk.x = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 0]) + bias_s[c + 4 * q + 0], ACT));
+                            pk.y = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 1]) + bias_s[c + 4 * q + 1], ACT));
+                            pk.z = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 2]) + bias_s[c + 4 * q + 2], ACT));
+                            pk.w = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 3]) + bias_s[c + 4 * q + 3], ACT));
                         } else {
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
                                 const unsigned raw = q < 4 ? r[8 * q + e] : r2[8 * (q - 4) + e];
-                                v[e] = gl_activate_bf16_grade(__uint_as_float(raw) + bias_s[c + 8 * q + e], g.act);
+                                v[e] = gl_activate_bf16_grade(__uint_as_float(raw) + bias_s[c + 8 * q + e], ACT);
                             }
                             __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
                             __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
@@ -248,9 +267,9 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     }
                     fence_proxy_async();
                     __syncwarp();
-                    if (lane == 0 && mrow0 < g.M && n0 + c < g.N) {
-                        if (out_mode == 2) tma_reduce_add_2d(&map_out, n0 + c, mrow0, patch_u32);
-                        else tma_store_2d(&map_out, n0 + c, mrow0, patch_u32);
+                    if (lane == 0 && mrow0 < g.M && n0 + c < N) {
+                        if (out_mode == 2) tma_reduce_add_2d(mo, n0 + c, mrow0, patch_u32);
+                        else tma_store_2d(mo, n0 + c, mrow0, patch_u32);
                         bulk_commit();
                     }
                 }
@@ -264,12 +283,12 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = __uint_as_float(r[j]);
                     __syncwarp();
                     const int n = n0 + c + lane;
-                    if (n < g.N) {
+                    if (n < N) {              // (element-wise results are never of a second set: N is g.N here)
                         const float bv = bias_s[c + lane];
                         const int rows_here = min(32, g.M - mrow0);
 #pragma unroll 4
                         for (int rr = 0; rr < rows_here; ++rr) {
-                            float v = gl_activate<false>(patch[rr * 33 + lane] + bv, g.act);
+                            float v = gl_activate<false>(patch[rr * 33 + lane] + bv, ACT);
                             const size_t o = (size_t)(mrow0 + rr) * g.N + n;
                             if (g.add0) v += g.add0[o];
                             if (g.add1) v += g.add1[o];
@@ -278,6 +297,13 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     }
                 }
             }
+            }
+            };
+            switch (act) {
+                case GL_ACT_GELU_TANH: store_tile(std::integral_constant<int, GL_ACT_GELU_TANH>{}); break;
+                case GL_ACT_GELU_ERF: store_tile(std::integral_constant<int, GL_ACT_GELU_ERF>{}); break;
+                case GL_ACT_RELU: store_tile(std::integral_constant<int, GL_ACT_RELU>{}); break;
+                default: store_tile(std::integral_constant<int, GL_ACT_NONE>{}); break;
             }
             tc_fence_before();
             __syncwarp();
@@ -354,7 +380,15 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
         rc = gl_cached_map(&map_out, g.out, (uint64_t)g.M, (uint64_t)g.N, 32, sizeof(TO) == 4 ? 32 : 64, (uint32_t)sizeof(TO));
         if (rc != GL_OK) return rc;
     }
-    const int tiles = ((g.M + MT * TG_BM - 1) / (MT * TG_BM)) * ((g.N + BN - 1) / BN);
+    CUtensorMap map_wB = map_w, map_outB = map_out;
+    if (g.wB) {
+        if (out_mode != 1 || g.a2 || (g.NB * sizeof(TO)) % 16 || ((uintptr_t)g.outB & 15)) return GL_ERR_SHAPE;
+        rc = gl_cached_map_bf16(&map_wB, g.wB, (uint64_t)g.NB, (uint64_t)g.K, BN, TG_BK);
+        if (rc != GL_OK) return rc;
+        rc = gl_cached_map(&map_outB, g.outB, (uint64_t)g.M, (uint64_t)g.NB, 32, sizeof(TO) == 4 ? 32 : 64, (uint32_t)sizeof(TO));
+        if (rc != GL_OK) return rc;
+    }
+    const int tiles = ((g.M + MT * TG_BM - 1) / (MT * TG_BM)) * ((g.N + BN - 1) / BN + (g.wB ? (g.NB + BN - 1) / BN : 0));
     // Tiles that fill the SMs unevenly are cut where the blocks' equal shares meet, if the epilogue can
     // add parts onto the output and every share still holds a fair run of k-blocks.
     const int k_blocks = (g.K + TG_BK - 1) / TG_BK + (g.a2 ? (g.K2 + TG_BK - 1) / TG_BK : 0);
@@ -367,7 +401,7 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 10 < sms * 7);
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
     if (gl_launch(gemm_tcgen05_kernel<BN, STAGES, TO, MT>, dim3(grid), dim3(TG_THREADS), smem, stream, 1, ga, map_a, map_w, map_a2, map_w2,
-                  map_out, out_mode, split) != 0)
+                  map_out, map_wB, map_outB, out_mode, split) != 0)
         return GL_ERR_LAUNCH;
     return GL_OK;
 }
@@ -404,6 +438,10 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
         if (!g.w2 || g.K2 <= 0 || g.K2 % 8) return GL_ERR_SHAPE;
         if (((uintptr_t)g.a2 | (uintptr_t)g.w2) & 15) return GL_ERR_ALIGN;
     }
+    if (g.wB) {
+        if (g.NB <= 0 || !g.outB || g.a2 || g.add0 || g.add1) return GL_ERR_SHAPE;
+        if ((uintptr_t)g.wB & 15) return GL_ERR_ALIGN;
+    }
     if (bn == 0) {
         // A tile's time goes with the operand bytes it pulls from L2, about (128 + width); the
         // grid runs in waves of one tile per SM, and the last wave counts whole.
@@ -420,7 +458,7 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
         for (int i = 0; i < 5; ++i) {
             const int c = cands[i];
             if (c == 160 && out_dtype != GL_F32) continue;
-            const int tiles = tm * ((g.N + c - 1) / c);
+            const int tiles = tm * ((g.N + c - 1) / c + (g.wB ? (g.NB + c - 1) / c : 0));
             // (tiles that will be cut into equal shares are not modelled here: the widest tile that
             // the rule below picks is also the one that cuts best)
             const long cost = (long)((tiles + sms - 1) / sms) * (TG_BM + c);

@@ -437,7 +437,9 @@ class _GemmArgs(Structure):
                 ("M", c_int), ("N", c_int), ("K", c_int), ("act", c_int),
                 # a second product summed into the same output (the tcgen05 kernel reads these; the
                 # other kernels' argument structs end before them)
-                ("a2", c_void_p), ("w2", c_void_p), ("bias2", c_void_p), ("K2", c_int)]
+                ("a2", c_void_p), ("w2", c_void_p), ("bias2", c_void_p), ("K2", c_int),
+                # a second set of columns from the same rows (tcgen05 kernel only)
+                ("wB", c_void_p), ("biasB", c_void_p), ("outB", c_void_p), ("NB", c_int), ("actB", c_int)]
 
 
 def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
@@ -456,7 +458,7 @@ def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
     if act not in ACTIVATIONS:
         raise KernelError(f"activation {act!r} unknown")
     return _GemmArgs(a.data_ptr(), w.data_ptr(), _addr(bias), _addr(add0), _addr(add1), out.data_ptr(),
-                     M, N, K, ACTIVATIONS[act], None, None, None, 0)
+                     M, N, K, ACTIVATIONS[act], None, None, None, 0, None, None, None, 0, 0)
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
@@ -521,11 +523,13 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
                  add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
-                 tile_n: int = 0, _defines=(), second=None) -> torch.Tensor:
+                 tile_n: int = 0, _defines=(), second=None, fork=None):
     """The tensor-core product (tcgen05.mma fed by TMA, accumulators in tensor memory) for
     bfloat16 operands with K a multiple of 8; meant for many rows.  ``second`` = (a2, w2, bias2)
     sums another product over the same rows and columns into the tile before the epilogue:
-    out = act(a·wᵀ + a2·w2ᵀ + bias + bias2) + add0 + add1."""
+    out = act(a·wᵀ + a2·w2ᵀ + bias + bias2) + add0 + add1.  ``fork`` = (wB, biasB, actB) computes a
+    second output actB(a·wBᵀ + biasB) in the same launch (nothing added, no ``second``; both
+    outputs' rows whole 16-byte units) and makes the result the pair (out, outB)."""
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     if out is None:
@@ -535,12 +539,22 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
         raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
     if second is not None:
         _second_product(g, a, w, second)
+    out_b = None
+    if fork is not None:
+        w_b, bias_b, act_b = fork
+        _need(w_b, "wB", torch.bfloat16)
+        if w_b.shape[1] != a.shape[1] or act_b not in ACTIVATIONS:
+            raise KernelError(f"second set of columns {tuple(w_b.shape)} does not fit a {tuple(a.shape)}")
+        if bias_b is not None:
+            _need(bias_b, "biasB", torch.float32, (w_b.shape[0],))
+        out_b = torch.empty((a.shape[0], w_b.shape[0]), dtype=out.dtype, device=a.device)
+        g.wB, g.biasB, g.outB, g.NB, g.actB = w_b.data_ptr(), _addr(bias_b), out_b.data_ptr(), w_b.shape[0], ACTIVATIONS[act_b]
     if tile_n not in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
         raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256; "
                           "1000 more for tiles of 256 rows (160, 192, 256)")
     fn = _lib("gemm_tcgen05.cu", _defines).gl_gemm_tcgen05
     _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(tile_n), _stream()), "gemm_tcgen05")
-    return out
+    return out if fork is None else (out, out_b)
 
 
 def wait_failures() -> dict:
@@ -571,6 +585,19 @@ def linear_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
             return gemm_tcgen05(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
     out = linear(a, w, bias, add0=add0, out_dtype=torch.float32, out=out)
     return linear(a2, w2, bias2, add0=out, out=out)
+
+
+def linear_fork(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], act,
+                w_b: torch.Tensor, bias_b: Optional[torch.Tensor], act_b, out_dtype: Optional[torch.dtype] = None):
+    """(act(a·wᵀ + bias), act_b(a·w_bᵀ + bias_b)): the first products of two branches that read the
+    same rows.  For many rows of bfloat16 both run as one grid of tensor-core tiles; otherwise one
+    after the other."""
+    dt = out_dtype or a.dtype
+    if (USE_TCGEN05 and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w_b.dtype == torch.bfloat16
+            and a.shape[0] > SKINNY_MAX_ROWS and a.shape[1] % 8 == 0
+            and (w.shape[0] * dt.itemsize) % 16 == 0 and (w_b.shape[0] * dt.itemsize) % 16 == 0):
+        return gemm_tcgen05(a, w, bias, act, out_dtype=dt, fork=(w_b, bias_b, act_b))
+    return linear(a, w, bias, act, out_dtype=dt), linear(a, w_b, bias_b, act_b, out_dtype=dt)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,

@@ -75,12 +75,15 @@ class Attention(Mixer):
         a1 = add[1] if len(add) > 1 else None
         return ops.linear(o, w, b, add0=a0, add1=a1, out=out)
 
-    def until_last(self, xn, ctx, cache):
+    def first_product(self):
+        return self.w_qkv, self.b_qkv, None
+
+    def until_last(self, xn, ctx, cache, first=None):
         """Everything but the output projection: the attention output [T, heads * head size] with the
-        projection's weight and bias."""
+        projection's weight and bias.  ``first``: the joined q, k, v projection if the caller made it."""
         s = self.spec
         T = xn.shape[0]
-        qkv = ops.linear(xn, self.w_qkv, self.b_qkv, out_dtype=ctx.act_dtype)
+        qkv = first if first is not None else ops.linear(xn, self.w_qkv, self.b_qkv, out_dtype=ctx.act_dtype)
         tables = self.position.tables(ctx)
         cos, sin = tables if tables is not None else (None, None)
         pages = ctx.pages[cache.group]

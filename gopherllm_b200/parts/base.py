@@ -99,6 +99,10 @@ class Mixer(Part):
     # Optional: ``until_last(xn, ctx, cache)`` -> (activations, weight, bias), everything but the last
     # product, for a block that runs the last products of its branches as one (ops.linear_pair).
     until_last = None
+    # Optional, with until_last: ``first_product()`` -> (weight, bias, activation) of the product that
+    # until_last starts with on xn; until_last then takes ``first=`` that product's result instead of
+    # computing it, so that a block can run the first products of its branches as one (ops.linear_fork).
+    first_product = None
 
     # A mixer that sets this accepts callables among ``add``: it calls them just before its last
     # product and adds what they return.  A block uses that to let another branch run beside the
@@ -111,9 +115,11 @@ class Mixer(Part):
 
 class FeedForward(Part):
     """forward(xn, ctx, add, out): out = ffn(xn) + sum(add), float32 [T, hidden].
-    Optional: until_last(xn, ctx) -> (activations, weight, bias), everything but the last product."""
+    Optional: until_last(xn, ctx) -> (activations, weight, bias), everything but the last product;
+    with it, first_product() -> (weight, bias, activation) and until_last(..., first=result), as for a mixer."""
 
     until_last = None
+    first_product = None
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

@@ -56,7 +56,14 @@ class ParallelBlock(_AssembledBlock):
             # else one after the other.  What comes before them runs on two streams in decode steps:
             # with few tokens every kernel is a stream of weights, and the feed-forward's first product
             # keeps memory busy while the mixer's small kernels start and finish.
-            if side is None:
+            if side is None and self.ffn.first_product is not None and self.mixer.first_product is not None:
+                # many tokens: the branches' first products read the same rows and run as one grid
+                wm, bm, am = self.mixer.first_product()
+                wf, bf, af = self.ffn.first_product()
+                ym, yf = ops.linear_fork(xn, wm, bm, am, wf, bf, af, ctx.act_dtype)
+                h, w2, b2 = self.ffn.until_last(xn, ctx, first=yf)
+                o, wo, bo = self.mixer.until_last(xn, ctx, cache, first=ym)
+            elif side is None:
                 h, w2, b2 = self.ffn.until_last(xn, ctx)
                 o, wo, bo = self.mixer.until_last(xn, ctx, cache)
             else:

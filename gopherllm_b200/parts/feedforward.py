@@ -35,8 +35,12 @@ class DenseFeedForward(FeedForward):
         self.w_up, self.w_down = t["up.weight"], t["down.weight"]
         self.b_up, self.b_down = t.get("up.bias"), t.get("down.bias")
 
-    def until_last(self, xn, ctx):
-        h = ops.linear(xn, self.w_up, self.b_up, act=self.spec.activation, out_dtype=ctx.act_dtype)
+    def first_product(self):
+        return self.w_up, self.b_up, self.spec.activation
+
+    def until_last(self, xn, ctx, first=None):
+        h = first if first is not None else ops.linear(xn, self.w_up, self.b_up, act=self.spec.activation,
+                                                       out_dtype=ctx.act_dtype)
         return h, self.w_down, self.b_down
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:

@@ -175,6 +175,34 @@ def test_gemm_tcgen05_two_products_one_tile(M, N, K1, K2):
     assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("M,N,NB,K", [(300, 200, 520, 96), (130, 528, 72, 1096), (2048, 7680, 10240, 2560)])
+def test_gemm_tcgen05_two_sets_of_columns(M, N, NB, K):
+    """(a w^T + b, act(a wB^T + bB)) from one launch: the tiles of the second set follow the first's,
+    each with its own bias, activation, width and output; against each product alone in 64-bit, and
+    bit for bit against the same kernel run once per set."""
+    o = ops()
+    a = rnd(M, K, dtype=torch.bfloat16)
+    w, wb = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1), rnd(NB, K, dtype=torch.bfloat16, scale=0.05, seed=4)
+    b, bb = rnd(N, seed=2), rnd(NB, seed=5)
+    want, want_b = ref_linear(a, w, b, None, None, None), ref_linear(a, wb, bb, "gelu_new", None, None)
+    for tile in (0, 64, 128, 192, 256, 1256):
+        y, yb = o.gemm_tcgen05(a, w, b, None, tile_n=tile, fork=(wb, bb, "gelu_new"))
+        torch.cuda.synchronize()
+        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        assert y.shape == (M, N) and yb.shape == (M, NB) and y.dtype == yb.dtype == torch.bfloat16
+        for got, ref in ((y, want), (yb, want_b)):
+            err = (got.double() - ref).abs().max().item()
+            assert err <= 2 ** -8 * max(1.0, ref.abs().max().item()), (tile, err)
+        assert torch.equal(y, o.gemm_tcgen05(a, w, b, None, tile_n=tile))
+        assert torch.equal(yb, o.gemm_tcgen05(a, wb, bb, "gelu_new", tile_n=tile))
+    y, yb = o.linear_fork(a, w, None, None, wb, bb, "gelu_new", torch.float32)       # 32-bit outputs, one bias missing
+    assert (y.double() - ref_linear(a, w, None, None, None, None)).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
+    assert (yb.double() - want_b).abs().max() <= 3e-5 * max(1.0, want_b.abs().max().item())
+    y, yb = o.linear_fork(a[:8], w, b, None, wb, bb, "gelu_new")                      # few rows: one after the other
+    assert (y.double() - want[:8]).abs().max() <= 2 ** -8 * max(1.0, want.abs().max().item())
+    assert (yb.double() - want_b[:8]).abs().max() <= 2 ** -8 * max(1.0, want_b.abs().max().item())
+
+
 def test_gemm_tcgen05_one_weight_stands_out():
     """A single large weight must reach exactly one output column, wherever it sits in K and N."""
     o = ops()
