@@ -157,6 +157,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                            cache.n_pages, cache.max_slots)
     results: List[Optional[GenerationResult]] = [None] * len(prompts)
     prepare = getattr(engine, "prepare_decode", None)
+    fetch = getattr(engine, "fetch", None) if prepare is not None else None
     for batch in batches:
         t_start = time.perf_counter()
         states = [SequenceState(prompts[i], options.max_tokens, options.stop_tokens, spec.max_positions)
@@ -177,11 +178,20 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                     rows_dev = torch.tensor(live, dtype=torch.int32).to(engine.device)
                 chosen = sampler.sample(logits, rows_dev)
                 # While the device finishes the step and samples: the next step's descriptor, if every
-                # sequence can go on (the tokens are filled in when they are known).
-                ahead = None
+                # sequence can go on.  An engine that can read its tokens on the device is given the
+                # sampler's output and starts that step at once, before the host has seen the tokens, so
+                # the device does not wait for the host between steps; should a sequence then end with
+                # a stop token, the step has merely fed one token too many to a sequence that is closed,
+                # and the rows of the others stand (a row does not depend on its neighbours).
+                ahead, ahead_logits, sampled = None, None, None
                 if prepare is not None and all(states[r].may_continue() for r in live):
                     ahead = prepare([slots[r] for r in live])
-                tokens = chosen.tolist()                                # waits for the step
+                    if fetch is not None:
+                        sampled = torch.cuda.Event()
+                        sampled.record()
+                        ahead_logits = engine.finish_decode(ahead, chosen)
+                        ahead = None
+                tokens = fetch(chosen, sampled) if sampled is not None else chosen.tolist()   # waits for the sampling
                 now = time.perf_counter()
                 if first:
                     t_prefill_end = now
@@ -189,12 +199,13 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                         stats[r].prefill_time = now - t_start
                         stats[r].ttft = now - t_start
                     first = False
-                nxt, runs = [], []
-                for r, tok in zip(live, tokens):
+                nxt, runs, kept = [], [], []
+                for i, (r, tok) in enumerate(zip(live, tokens)):
                     stats[r].token_times.append(now - t_start)
                     if states[r].accept(tok):
                         nxt.append(r)
                         runs.append((slots[r], [tok]))
+                        kept.append(i)
                     else:
                         engine.close(slots[r])
                         slots[r] = None
@@ -207,7 +218,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                     canceled = True
                     break
                 if runs:
-                    if ahead is not None and len(runs) == len(tokens):
+                    if ahead_logits is not None:
+                        logits = ahead_logits if len(kept) == len(tokens) else \
+                            ahead_logits.index_select(0, torch.tensor(kept, dtype=torch.int64).to(engine.device))
+                    elif ahead is not None and len(runs) == len(tokens):
                         logits = engine.finish_decode(ahead, tokens)
                     else:
                         logits = engine.step(runs)

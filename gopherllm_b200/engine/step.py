@@ -85,6 +85,8 @@ class Engine:
         self._graph_pool = None
         self.overlap_branches = True                         # decode steps run parallel branches on two streams
         self._side_stream = None
+        self._copy_stream = None
+        self._fetch_pin = None
         self.launches_per_loop_step: Dict[int, int] = {}    # kernels in one captured decode_loop step, by batch
         self._pinned: List[Optional[torch.Tensor]] = [None, None]
         self._events: List[Optional[torch.cuda.Event]] = [None, None]
@@ -206,10 +208,17 @@ class Engine:
         lay, buf, meta = self.plan([(s, (0,)) for s in slots], None)
         return lay, self._stage(buf), meta
 
-    def finish_decode(self, handle, tokens: Sequence[int]) -> torch.Tensor:
+    def finish_decode(self, handle, tokens) -> torch.Tensor:
+        """Launch a prepared one-token step.  ``tokens``: one id per sequence from the host, or an
+        int32 tensor on the device (a sampler's output): the step then reads its tokens where the
+        sampler left them, so it can be launched before the host has seen them."""
         lay, pin, meta = handle
-        toks = np.asarray(tokens, dtype=np.int64)
         o, n = lay.off["tokens"]
+        if isinstance(tokens, torch.Tensor):
+            if tokens.dtype != torch.int32 or tokens.shape != (n,) or tokens.device != self.device:
+                raise ValueError(f"{n} int32 tokens on {self.device} expected, one per sequence")
+            return self._launch(lay, pin, meta, tokens_dev=tokens)
+        toks = np.asarray(tokens, dtype=np.int64)
         if toks.shape != (n,):
             raise ValueError(f"{n} tokens expected, one per sequence")
         if toks.min() < 0 or toks.max() >= self.vocab:
@@ -217,12 +226,33 @@ class Engine:
         pin.numpy()[o:o + n] = toks
         return self._launch(lay, pin, meta)
 
-    def _launch(self, lay: _Layout, pin: torch.Tensor, meta: dict) -> torch.Tensor:
+    def fetch(self, values: torch.Tensor, after: "torch.cuda.Event") -> List[int]:
+        """A small device tensor as a host list, copied on a stream of its own once ``after`` has
+        happened: work queued behind ``after`` on the main stream does not hold the copy up."""
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        n = values.numel()
+        if self._fetch_pin is None or self._fetch_pin.numel() < n or self._fetch_pin.dtype != values.dtype:
+            self._fetch_pin = torch.empty(max(n, 1024), dtype=values.dtype, pin_memory=True)
+        s = self._copy_stream
+        s.wait_event(after)
+        with torch.cuda.stream(s):
+            self._fetch_pin[:n].copy_(values.reshape(-1), non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(s)
+        done.synchronize()
+        return self._fetch_pin[:n].tolist()
+
+    def _launch(self, lay: _Layout, pin: torch.Tensor, meta: dict,
+                tokens_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
         graph = None
         if self.use_graphs and meta["is_decode"] and lay.B <= self.graph_max_batch:
             graph = self._decode_graph(lay, meta)
+        o, n = lay.off["tokens"]
         if graph is not None:
             graph.desc.copy_(pin, non_blocking=True)
+            if tokens_dev is not None:
+                graph.desc[o:o + n].copy_(tokens_dev)
             self._staged_done()
             graph.first.replay()
             if graph.graph is not None:
@@ -231,6 +261,8 @@ class Engine:
         else:
             dev = torch.empty(lay.size, dtype=torch.int32, device=self.device)
             dev.copy_(pin, non_blocking=True)
+            if tokens_dev is not None:
+                dev[o:o + n].copy_(tokens_dev)
             self._staged_done()
             logits = self.model.forward(self.context(lay, dev, meta), self.cache)
         for s, n in zip(meta["slots"], meta["new_lens"]):

@@ -93,6 +93,38 @@ def test_unequal_prompts_stops_and_batches_one_after_another():
         m.generate([[]], max_tokens=5, **GREEDY)
 
 
+def test_stop_tokens_in_bfloat16_batches():
+    """The bfloat16 engine starts each next step from the sampler's output before the host has seen the
+    tokens; a sequence that meets a stop token then has been fed once too often and is dropped, the
+    others go on.  Every token of every result must be the plain argmax given the result's own prefix
+    (within rounding), a "stop" must come where the stop token is the argmax, and nothing stays held."""
+    name = "B"
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(35)
+    prompts = [tiny.prompt(rng, n, cfg["vocab_size"]) for n in (7, 21, 2, 40, 13)]
+    m = model(name, "bfloat16", max_tokens=5 * 128)
+    alone = m.generate(prompts[1], max_tokens=16, stop_tokens=(), **GREEDY).tokens
+    stop = alone[5]
+    res = m.generate(prompts, max_tokens=16, stop_tokens=(stop,), **GREEDY)
+    pcfg, W = plain_phi.read_folder(tiny.folder(name))
+    tol = 2 * tiny.TOL["bfloat16"]
+    assert any(r.finish_reason == "stop" for r in res) and any(r.finish_reason == "length" for r in res)
+    for p, r in zip(prompts, res):
+        assert stop not in r.tokens
+        ref = plain_phi.phi_logits(p + r.tokens, W, pcfg).numpy()
+        for i, tok in enumerate(r.tokens):
+            row = ref[len(p) + i - 1]
+            assert row[tok] >= row.max() - tol * max(1.0, np.abs(row).max()), i
+        if r.finish_reason == "stop":
+            row = ref[len(p) + len(r.tokens) - 1]
+            assert row[stop] >= row.max() - tol * max(1.0, np.abs(row).max())
+        else:
+            assert r.finish_reason == "length" and len(r.tokens) == 16
+    cache = m.engine.cache
+    cache.check()
+    assert cache.slots.held_count == 0 and all(g.pool.held_count == 0 for g in cache.groups)
+
+
 def test_sampling_is_seeded_and_independent_of_the_batch():
     name = "B"
     cfg = tiny.TINY[name][0]
