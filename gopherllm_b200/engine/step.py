@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.sequence_cache import SequenceCache
+from ..cache.sequence_cache import PAGE, SequenceCache
 from .model import DecoderModel
 
 
@@ -270,12 +270,22 @@ class Engine:
         return logits
 
     # -- CUDA graphs for decode steps -------------------------------------------
+    def _length_bucket(self, longest: int) -> int:
+        """Sequence lengths share a captured step by bucket (4, 8, 16, ... pages, at most the cache's
+        longest sequence): how a kernel cuts its work may depend on the length (the splits of decode
+        attention), never whether its result is right, so a bucket's graph is sized for its upper end."""
+        pages = 4
+        while pages * PAGE < longest:
+            pages *= 2
+        return min(pages * PAGE, self.cache.max_positions)
+
     def _decode_graph(self, lay: _Layout, meta: dict):
         """The captured step for this batch shape, or None the first time the shape is
         seen (that step runs kernel by kernel, which also loads and warms every kernel).
         The logits of a replayed step live in the graph's own buffer until the next
         replay of the same shape."""
-        key = lay.key()
+        bucket = self._length_bucket(max(meta["new_lens"]))
+        key = lay.key() + (bucket,)
         g = self._graphs.get(key)
         if g is None:
             self._graphs[key] = False
@@ -284,7 +294,7 @@ class Engine:
             g = _CapturedStep()
             g.desc = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
             bound = dict(meta)
-            bound["new_lens"] = [self.cache.max_positions]      # launch sizes must hold for any length
+            bound["new_lens"] = [bucket]                        # launch sizes are chosen for the bucket's longest
             ctx = self.context(lay, g.desc, bound)
             torch.cuda.synchronize(self.device)
             if self._graph_pool is None:
@@ -326,7 +336,8 @@ class Engine:
         cache.reserve([(s, c + steps) for s, c in zip(slots, ctxs)])
         lay, buf, meta = self.plan([(s, [t]) for s, t in zip(slots, tokens)], None)
         pin = self._stage(buf)
-        key = ("loop",) + lay.key()
+        bucket = self._length_bucket(max(ctxs) + steps)
+        key = ("loop",) + lay.key() + (bucket,)
         g = self._graphs.get(key)
         if g is None:
             g = _CapturedStep()
@@ -336,7 +347,7 @@ class Engine:
             g.history = torch.zeros((g.history_cap, B), dtype=torch.int32, device=self.device)
             g.state_row = torch.arange(B, dtype=torch.int32, device=self.device)
             bound = dict(meta)
-            bound["new_lens"] = [cache.max_positions]
+            bound["new_lens"] = [bucket]
             ctx = self.context(lay, g.desc, bound)
 
             def body():

@@ -332,12 +332,19 @@ def decode_blocks_per_sm(head_dim: int, group: int = 1) -> int:
 
 def decode_splits(batch: int, num_kv_heads: int, max_len: int, device, head_dim: int = 80,
                   group: int = 1) -> int:
-    """How many blocks share one (sequence, key/value head): as many as keep the whole
-    grid resident at once (a grid a little larger than the machine would run a second,
-    nearly empty wave), never more than the longest sequence has pages."""
+    """How many blocks share one (sequence, key/value head).  Never more blocks than are resident
+    at once (a grid a little larger than the machine would run a second, nearly empty wave), never
+    more than the longest sequence has pages.  Within that: enough blocks to put about 1.7 on every
+    SM, and enough that a block has at most 8 pages to walk through; more blocks than that only
+    take the SMs' shared memory from the products that run beside a short attention.  Measured on
+    Phi-2 shapes (32 heads of 80, 148 SMs; batches of 2 to 8, 512 to 2,048 positions) this is
+    within 3 % of the best split everywhere and up to 11 % a step better than filling every slot."""
     pages = max(1, -(-max_len // PAGE))
-    slots = sm_count(device) * decode_blocks_per_sm(head_dim, group)
-    return max(1, min(slots // max(1, batch * num_kv_heads), pages, 8))
+    sms = sm_count(device)
+    per = max(1, batch * num_kv_heads)
+    slots = sms * decode_blocks_per_sm(head_dim, group)
+    want = max(-(-(17 * sms // 10) // per), -(-pages // 8))
+    return max(1, min(want, slots // per, pages, 8))
 
 
 def decode_takes_qkv(act_dtype, cache_dtype, head_dim: int, rotary_half: int, interleaved: bool,
