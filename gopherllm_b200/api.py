@@ -114,10 +114,12 @@ def load(path: str, dtype="bfloat16", max_tokens: Optional[int] = None, device="
     t0 = time.time()
     arch, config = load_config(path)
     model = build_model(arch, config)
-    table = tensor_table(model.parameters(), arch.tensor_names(config))
+    names = arch.tensor_names(config)
+    table = tensor_table(model.parameters(), names)
     ignore = ("lm_head.weight",) if model.spec.tie_embeddings else ()
+    fused = names.fused() if hasattr(names, "fused") else None
     with torch.cuda.device(device):
-        tensors, nbytes = load_folder(path, table, cdt, device, ignore=ignore, progress=log)
+        tensors, nbytes = load_folder(path, table, cdt, device, ignore=ignore, progress=log, fused=fused)
         model.load(tensors)
         del tensors
         if max_tokens is None:

@@ -169,6 +169,16 @@ class PhiTensorNames:
         role = f"{slot}.{prefix}" if prefix else slot
         return self._layer[role].format(i=i) + "." + suffix
 
+    def fused(self) -> dict:
+        """Tensors a file may hold fused: the three projections as one matrix (and one bias) with rows
+        ordered Q, K, V, as the reference takes blk.N.attn_qkv in place of attn_q/k/v (model.go:2046-2065)."""
+        out = {}
+        for i in range(self.cfg.num_hidden_layers):
+            base = f"model.layers.{i}.self_attn."
+            for suffix in ("weight", "bias"):
+                out[f"{base}Wqkv.{suffix}"] = [f"{base}{p}_proj.{suffix}" for p in ("q", "k", "v")]
+        return out
+
 
 register_architecture(
     Architecture(name="phi", config_class=PhiConfig, build_spec=phi_model_spec,

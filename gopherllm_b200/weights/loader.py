@@ -17,7 +17,7 @@ from typing import Callable, Dict, Iterator, List, Optional, Tuple
 import torch
 
 from ..parts.base import ParamSpec
-from .safetensors_io import TensorFile, index_folder, write_file
+from .safetensors_io import TensorEntry, TensorFile, index_folder, write_file
 
 STORAGE_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16,
                   "bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}
@@ -72,12 +72,45 @@ def resident_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype) -
     return torch.bfloat16 if stored == torch.bfloat16 else torch.float32
 
 
-def check_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], ignore: Tuple[str, ...] = ()):
+def split_fused(entries: Dict[str, TensorEntry], table: Dict[str, Tuple[str, ParamSpec]],
+                fused: Optional[Dict[str, List[str]]], wrong: List[str]) -> Dict[str, TensorEntry]:
+    """A file may hold several declared tensors as one, their rows one after the other (the reference
+    takes a fused attn_qkv or split attn_q/k/v, whichever the file has, model.go:2046-2065, and cuts a
+    fused bias by row ranges, model.go:2222-2227).  ``fused``: file tensor name -> names of the declared
+    tensors it holds, in row order.  Where the fused tensor is present and none of its parts is, the
+    parts become entries of their own that point into its bytes (rows are contiguous in the file)."""
+    if not fused:
+        return entries
+    entries = dict(entries)
+    for fname, parts in fused.items():
+        e = entries.get(fname)
+        if e is None or any(p in entries for p in parts) or any(p not in table for p in parts):
+            continue
+        shapes = [tuple(table[p][1].shape) for p in parts]
+        rows = sum(s[0] for s in shapes)
+        if any(s[1:] != e.shape[1:] for s in shapes) or e.shape[0] != rows:
+            wrong.append(f"{fname} is {list(e.shape)}, the model wants {[rows, *shapes[0][1:]]} "
+                         f"(the rows of {', '.join(parts)})")
+            del entries[fname]
+            for p, s in zip(parts, shapes):               # reported once, as the fused tensor
+                entries[p] = TensorEntry(p, e.dtype, s, e.begin, e.begin, e.file)
+            continue
+        row_bytes = (e.end - e.begin) // max(1, e.shape[0])
+        at = e.begin
+        for p, s in zip(parts, shapes):
+            entries[p] = TensorEntry(p, e.dtype, s, at, at + s[0] * row_bytes, e.file)
+            at += s[0] * row_bytes
+        del entries[fname]
+    return entries
+
+
+def check_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], ignore: Tuple[str, ...] = (),
+                 fused: Optional[Dict[str, List[str]]] = None):
     """Compare the folder's tensor table with what the model declares."""
-    entries = index_folder(folder)
+    wrong: List[str] = []
+    entries = split_fused(index_folder(folder), table, fused, wrong)
     missing = sorted(n for n, (_, spec) in table.items() if n not in entries and not spec.optional)
     unexpected = sorted(n for n in entries if n not in table and n not in ignore)
-    wrong = []
     for n, (_, spec) in sorted(table.items()):
         e = entries.get(n)
         if e is None:
@@ -92,10 +125,10 @@ def check_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], ignore: T
 
 
 def load_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], compute: torch.dtype, device,
-                ignore: Tuple[str, ...] = (), progress: Optional[Callable[[str], None]] = None
-                ) -> Tuple[Dict[str, torch.Tensor], int]:
+                ignore: Tuple[str, ...] = (), progress: Optional[Callable[[str], None]] = None,
+                fused: Optional[Dict[str, List[str]]] = None) -> Tuple[Dict[str, torch.Tensor], int]:
     """Tensors by model parameter key, on ``device``; and the bytes read."""
-    entries = check_folder(folder, table, ignore)
+    entries = check_folder(folder, table, ignore, fused)
     out: Dict[str, torch.Tensor] = {}
     nbytes = 0
     with TensorFile(entries) as tf:

@@ -124,6 +124,38 @@ def test_tied_head_may_lack_its_bias_and_carry_a_copy():
     assert torch.count_nonzero(tensors["head/bias"]) == 0
 
 
+def test_fused_projections_are_taken_in_place_of_split_ones():
+    """A file with the three projections of a layer as one matrix and one bias (rows Q, K, V) loads to
+    the same tensors as the split file; a fused tensor with the wrong number of rows is one clear line."""
+    src = tiny.folder("B")                                        # grouped heads: q, k and v differ in rows
+    arch, cfg = load_config(src)
+    model, table = table_for(src)
+    fused = arch.tensor_names(cfg).fused()
+    want, _ = load_folder(src, table, torch.float32, "cpu")
+
+    def fuse(t, layers, drop_rows=0):
+        for i in layers:
+            base = f"model.layers.{i}.self_attn."
+            for suffix in ("weight", "bias"):
+                parts = [t.pop(f"{base}{p}_proj.{suffix}") for p in ("q", "k", "v")]
+                whole = torch.cat(parts, dim=0)
+                t[f"{base}Wqkv.{suffix}"] = whole[:whole.shape[0] - drop_rows].contiguous()
+    n_layers = cfg.num_hidden_layers
+    d = rewrite(src, lambda t: fuse(t, range(n_layers)))
+    with pytest.raises(WeightsError):
+        check_folder(d, table)                                    # not told about fused tensors: unknown names
+    got, _ = load_folder(d, table, torch.float32, "cpu", fused=fused)
+    assert set(got) == set(want) and all(torch.equal(got[k], want[k]) for k in want)
+    d = rewrite(src, lambda t: fuse(t, [0]))                      # one layer fused, the others split
+    got, _ = load_folder(d, table, torch.float32, "cpu", fused=fused)
+    assert all(torch.equal(got[k], want[k]) for k in want)
+    d = rewrite(src, lambda t: fuse(t, [1], drop_rows=1))
+    with pytest.raises(WeightsError) as e:
+        check_folder(d, table, fused=fused)
+    assert not e.value.missing and not e.value.unexpected and len(e.value.wrong) == 2
+    assert "model.layers.1.self_attn.Wqkv.weight is [" in str(e.value) and "the rows of" in str(e.value)
+
+
 def test_resident_types():
     m, v, i = ParamSpec((2, 2)), ParamSpec((2,), "vector"), ParamSpec((2,), "table_int")
     bf, f32, f16 = torch.bfloat16, torch.float32, torch.float16
