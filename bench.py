@@ -2,6 +2,8 @@
 """Decode and prefill throughput of the Phi-2 sized model with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L]
+    python bench.py --model phi-1.5          the same measurements at Phi-1.5's layer sizes
+    python bench.py --ragged                 64 unequal prompts as one batch through Model.generate
 
 Prints one JSON line.  ``value`` is decoded tokens a second at the given batch and
 context, timed on the device over K decode steps that run back to back without the
@@ -28,6 +30,9 @@ PHI2 = dict(architectures=["PhiForCausalLM"], model_type="phi", num_hidden_layer
             partial_rotary_factor=0.4, rope_theta=10000.0, layer_norm_eps=1e-5, hidden_act="gelu_new",
             qk_layernorm=False, tie_word_embeddings=False, max_position_embeddings=2048,
             initializer_range=0.02, torch_dtype="bfloat16")
+# Phi-1.5 sizes (Phi-1 has the same layer shapes)
+PHI15 = dict(PHI2, num_hidden_layers=24, hidden_size=2048, intermediate_size=8192, partial_rotary_factor=0.5)
+MODELS = {"phi-2": ("Phi-2", PHI2, 2), "phi-1.5": ("Phi-1.5", PHI15, 3)}      # label, sizes, seed of the weights
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -102,6 +107,10 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="leave out prefill, batch 1 and batch 64")
     ap.add_argument("--sections", default="decode,e2e,prefill,points",
                     help="which measurements to run (for profiling a part): decode,e2e,prefill,points")
+    ap.add_argument("--model", default="phi-2", choices=sorted(MODELS), help="whose layer sizes to run")
+    ap.add_argument("--ragged", action="store_true",
+                    help="instead: 64 prompts of 16..1536 tokens as one batch through Model.generate, 512 tokens "
+                         "each at temperature 0.8, and a 32-bit check of 4 of them")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -125,12 +134,15 @@ def main():
     from gopherllm_b200.sampling.sampler import DeviceSampler, SamplerConfig, request_seed
 
     pk, pk_src = peaks()
-    cfg = dict(PHI2)
+    label, sizes, weight_seed = MODELS[args.model]
+    cfg = dict(sizes)
     layers_full = cfg["num_hidden_layers"]
     layers = args.layers or layers_full
+    if args.ragged:
+        return ragged(args, label, cfg, weight_seed, layers, layers_full)
     K, W, B, C = args.steps, args.warmup, args.batch, args.context
     max_b = max(B, 64) if "points" in sections else B
-    model = gl.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max_b * C, layers=layers)
+    model = gl.load_random(cfg, seed=weight_seed, dtype="bfloat16", max_tokens=max_b * C, layers=layers)
     eng = model.engine
     spec = model.spec
     rng = np.random.default_rng(4)
@@ -191,16 +203,16 @@ def main():
     step_bytes = weight_bytes + B * ctx_mid * kv_per_pos
     achieved = step_bytes / (ms_step / 1e3) / 1e9 if "decode" in sections else 0.0
     out = {
-        "metric": "decode tok/s at batch 8, context 2048 (Phi-2 sizes, bf16)" if (B, C) == (8, 2048)
-                  else f"decode tok/s at batch {B}, context {C} (Phi-2 sizes, bf16)",
+        "metric": f"decode tok/s at batch {B}, context {C} ({label} sizes, bf16)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4) if "decode" in sections else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, token ids uniform in [0,51200)",
-        "config": {"model": "Phi-2 sizes (PhiForCausalLM)", "layers": layers, "layers_of_model": layers_full,
+        "dtype": "bf16", "data": f"synthetic: random weights N(0,0.02) seed {weight_seed}, token ids uniform in [0,51200)",
+        "config": {"model": f"{label} sizes (PhiForCausalLM)", "layers": layers, "layers_of_model": layers_full,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "rotary_dim": int(cfg["partial_rotary_factor"] * 80), "global_batch": B, "seq_len": C,
+                   "rotary_dim": int(cfg["partial_rotary_factor"] * (cfg["hidden_size"] // cfg["num_attention_heads"])),
+                   "global_batch": B, "seq_len": C,
                    "context_at_timed_steps": f"{C - K - 1}..{C - 1}", "parallelism": "single GPU",
                    "sampling": "greedy", "l2": "each step reads weights and cache far larger than L2 (126 MB)",
                    "peaks": pk_src},
@@ -236,6 +248,66 @@ def main():
         b64, _, _ = decode_rate(64, min(K, 32), W, C)
         out["points"] = {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)}
     print(json.dumps(out))
+    return 0
+
+
+def ragged(args, label, cfg, weight_seed, layers, layers_full):
+    """A batch of unequal prompts through the entry point: 64 sequences that start together, lengths uniform
+    in [16, 1536] (seed 4), one step for all prompts, then 512 tokens each at temperature 0.8 (seed 5); and
+    the last prompt position's logits of 4 of the sequences in bfloat16 against the 32-bit path."""
+    import numpy as np
+    import torch
+    import gopherllm_b200 as gl
+    B, N, n_check = 64, 512, 4
+    rng = np.random.default_rng(4)
+    V = cfg["vocab_size"]
+    lens = [int(n) for n in rng.integers(16, 1537, size=B)]
+    prompts = [[int(t) for t in rng.integers(0, V, size=n)] for n in lens]
+    model = gl.load_random(cfg, seed=weight_seed, dtype="bfloat16", max_tokens=B * 2048, layers=layers)
+    opts = dict(max_tokens=N, temperature=0.8, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0,
+                stop_tokens=(), seed=5)
+    model.generate(prompts, **opts)                        # warm-up: loads the kernels, captures the steps
+    clocks = ClockSampler()
+    clocks.start()
+    res = model.generate(prompts, **opts)
+    clock_info = clocks.stop()
+    generated = sum(r.stats.generated_tokens for r in res)
+    prefill_s = max(r.stats.prefill_time for r in res)
+    total_s = max(r.stats.total_time for r in res)
+    # 32-bit check: the logits after the prompt, for the first sequences, both ways
+    eng = model.engine
+    got = []
+    for p in prompts[:n_check]:
+        s = eng.open()
+        got.append(eng.step([(s, p)])[0].float().cpu())
+        eng.close(s)
+    model.close()
+    del model, eng
+    torch.cuda.empty_cache()
+    m32 = gl.load_random(cfg, seed=weight_seed, dtype="float32", max_tokens=2048, layers=layers)
+    diff, scale, same = 0.0, 0.0, 0
+    for p, g in zip(prompts[:n_check], got):
+        s = m32.engine.open()
+        want = m32.engine.step([(s, p)])[0].cpu()
+        m32.engine.close(s)
+        diff = max(diff, float((g - want).abs().max()))
+        scale = max(scale, float(want.abs().max()))
+        same += int(int(g.argmax()) == int(want.argmax()))
+    print(json.dumps({
+        "metric": f"generated tok/s of a ragged batch of {B} ({label} sizes, bf16, through Model.generate)",
+        "value": round(generated / (total_s - prefill_s), 1), "unit": "tokens/s", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16",
+        "data": f"synthetic: random weights N(0,0.02) seed {weight_seed}, prompt lengths uniform in [16,1536] seed 4, "
+                "token ids uniform in [0,51200), temperature 0.8 seed 5",
+        "config": {"model": f"{label} sizes (PhiForCausalLM)", "layers": layers, "layers_of_model": layers_full,
+                   "global_batch": B, "prompt_tokens": sum(lens), "longest_prompt": max(lens),
+                   "new_tokens_each": N, "cache_positions_per_slot": 2048, "timing": "host clock around the entry point"},
+        "generated_tokens": generated, "decode_s": round(total_s - prefill_s, 4),
+        "prefill": {"tokens": sum(lens), "ms": round(prefill_s * 1e3, 2), "value": round(sum(lens) / prefill_s, 1)},
+        "clocks": clock_info,
+        "fp32_check": {"sequences": n_check, "max_abs_diff": round(diff, 5), "max_abs_logit": round(scale, 4),
+                       "argmax_equal": same},
+    }))
     return 0
 
 
