@@ -82,6 +82,19 @@ struct TgWork {
     }
 };
 
+// Tile number -> (row tile, column tile).  Tiles are numbered group by group: a group is `group` row tiles
+// by all column tiles, row tile fastest.  Blocks work on neighbouring numbers at the same time, so within a
+// group they share one weight tile and a few activation tiles, and the group's activations stay in L2
+// while the weights stream past; without groups (all row tiles fastest) a matrix of activations larger
+// than L2 would come from memory once per column tile.
+__device__ __forceinline__ void tg_tile_coords(int tile, int tiles_m, int tiles_n_all, int group, int& mt, int& nt) {
+    const int per_group = group * tiles_n_all;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int rows = min(group, tiles_m - g * group);
+    nt = r / rows;
+    mt = g * group + (r - nt * rows);
+}
+
 // K-major operand tile of 128-byte rows (64 bf16 of K), 128-byte swizzle
 __device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) { return umma_tile_desc(smem_addr, 128); }
 __host__ __device__ constexpr uint32_t umma_idesc(int bn) { return umma_idesc_bf16(bn, 0); }
@@ -95,7 +108,7 @@ __global__ void __launch_bounds__(TG_THREADS, 1)
 gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_w2,
                     const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_wB,
-                    const __grid_constant__ CUtensorMap map_outB, int out_mode, int split) {
+                    const __grid_constant__ CUtensorMap map_outB, int out_mode, int split, int group) {
     extern __shared__ unsigned char smem_raw[];
     constexpr int A_BYTES = MT * TG_BM * 128, B_BYTES = BN * 128, STAGE = A_BYTES + B_BYTES;
     constexpr int NBUF = 2 * MT * BN <= 512 ? 2 : 1;                                      // accumulator sets
@@ -112,7 +125,8 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
     const unsigned bar_tempty = bar_tfull + 16;               // [2] accumulator drained
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (g.M + MT * TG_BM - 1) / (MT * TG_BM), tiles_n = (g.N + BN - 1) / BN;
-    const int n_tiles = tiles_m * (tiles_n + (g.wB ? (g.NB + BN - 1) / BN : 0));     // the second set's tiles follow the first's
+    const int tiles_n_all = tiles_n + (g.wB ? (g.NB + BN - 1) / BN : 0);            // the second set's tiles follow the first's
+    const int n_tiles = tiles_m * tiles_n_all;
     const int k1_blocks = (g.K + TG_BK - 1) / TG_BK;                   // k-blocks of the first product
     const int k_blocks = k1_blocks + (g.a2 ? (g.K2 + TG_BK - 1) / TG_BK : 0);
 
@@ -141,8 +155,10 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
             int it = 0, tile, kb0, kb1;
             TgWork work(n_tiles, k_blocks, split);
             while (!failed && work.next(tile, kb0, kb1)) {
-                const bool fork = tile / tiles_m >= tiles_n;
-                const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m - (fork ? tiles_n : 0)) * BN;
+                int mt, nt;
+                tg_tile_coords(tile, tiles_m, tiles_n_all, group, mt, nt);
+                const bool fork = nt >= tiles_n;
+                const int m0 = mt * MT * TG_BM, n0 = (nt - (fork ? tiles_n : 0)) * BN;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, ((it / STAGES) - 1) & 1)) { failed = 1; break; }
@@ -206,8 +222,10 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
         TgWork work(n_tiles, k_blocks, split);
         for (; work.next(tile, kb0, kb1); ++local) {
             const int buf = local % NBUF, use = local / NBUF;
-            const bool fork = tile / tiles_m >= tiles_n;
-            const int m0 = (tile % tiles_m) * MT * TG_BM, n0 = (tile / tiles_m - (fork ? tiles_n : 0)) * BN;
+            int mt, nt;
+            tg_tile_coords(tile, tiles_m, tiles_n_all, group, mt, nt);
+            const bool fork = nt >= tiles_n;
+            const int m0 = mt * MT * TG_BM, n0 = (nt - (fork ? tiles_n : 0)) * BN;
             const int N = fork ? g.NB : g.N, act = fork ? g.actB : g.act;
             const float* bias = fork ? g.biasB : g.bias;
             const CUtensorMap* mo = fork ? &map_outB : &map_out;
@@ -400,8 +418,12 @@ static int launch_tg(const GemmArgs& g, cudaStream_t stream) {
     // of the SMs would have a tile, since part of the machine would otherwise stream all the weights)
     const int split = can_split && (tg_split_mode > 0 || (tg_split_mode < 0 && uneven && k_blocks >= 64) || tiles * 10 < sms * 7);
     const int grid = split ? sms : (tiles < sms ? tiles : sms);
+    // row tiles of a group: as many as keep the group's activations (all of K) within 28 MB
+    const long long a_tile_bytes = (long long)MT * TG_BM * (g.K + (g.a2 ? g.K2 : 0)) * 2;
+    int group = (int)((28LL << 20) / a_tile_bytes);
+    group = group < 1 ? 1 : group;
     if (gl_launch(gemm_tcgen05_kernel<BN, STAGES, TO, MT>, dim3(grid), dim3(TG_THREADS), smem, stream, 1, ga, map_a, map_w, map_a2, map_w2,
-                  map_out, map_wB, map_outB, out_mode, split) != 0)
+                  map_out, map_wB, map_outB, out_mode, split, group) != 0)
         return GL_ERR_LAUNCH;
     return GL_OK;
 }

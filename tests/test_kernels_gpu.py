@@ -80,7 +80,8 @@ def test_gemm_skinny(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (65, 40, 160), (200, 1000, 200),
-                                   (300, 777 * 8, 416), (2048, 2560, 2560), (1000, 7680, 2568)])
+                                   (300, 777 * 8, 416), (2048, 2560, 2560), (1000, 7680, 2568),
+                                   (6405, 200, 2560)])      # (rows enough for several groups of row tiles, the last one partial)
 def test_gemm_tcgen05(M, N, K):
     o = ops()
     a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
@@ -175,7 +176,8 @@ def test_gemm_tcgen05_two_products_one_tile(M, N, K1, K2):
     assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
 
 
-@pytest.mark.parametrize("M,N,NB,K", [(300, 200, 520, 96), (130, 528, 72, 1096), (2048, 7680, 10240, 2560)])
+@pytest.mark.parametrize("M,N,NB,K", [(300, 200, 520, 96), (130, 528, 72, 1096), (2048, 7680, 10240, 2560),
+                                      (5700, 136, 328, 2560)])
 def test_gemm_tcgen05_two_sets_of_columns(M, N, NB, K):
     """(a w^T + b, act(a wB^T + bB)) from one launch: the tiles of the second set follow the first's,
     each with its own bias, activation, width and output; against each product alone in 64-bit, and
