@@ -113,64 +113,69 @@ __global__ void qkv_cache_kernel(QkvCacheArgs a) {
     }
 }
 
-// The same for bfloat16 rows and cache without a head norm, one thread per 16-byte chunk (8
-// dims) of a head: the chunk and, inside the rotary part, its partner chunk are loaded with
-// 16-byte loads and the result leaves with one 16-byte store.  Needs the head size and the
-// rotary half to be multiples of 8 and split-half pairing.
+// The same for bfloat16 rows and cache without a head norm, one 16-byte chunk (8 dims) of a head at a
+// time: the chunk and, inside the rotary part, its partner chunk are loaded with 16-byte loads and the
+// result leaves with one 16-byte store.  One block per token, its threads over the token's chunks: what
+// depends on the token alone (position, page, angle rows) is looked up once, and a chunk's place costs
+// one 32-bit division (a flat index over all tokens cost three 64-bit ones a chunk and made the kernel
+// instruction-bound).  Needs the head size and the rotary half to be multiples of 8 and split-half pairing.
 __global__ void __launch_bounds__(256)
 qkv_cache_bf16_kernel(QkvCacheArgs a) {
     gl_grid_launch_dependents();
     gl_grid_wait();
-    const int chunks = a.hd >> 3, heads = a.nH + 2 * a.nKV;
-    const long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (id >= (long long)a.T * heads * chunks) return;
-    const int c = (int)(id % chunks);
-    const int j = (int)((id / chunks) % heads);
-    const int t = (int)(id / ((long long)chunks * heads));
-    const int kind = j < a.nH ? 0 : (j < a.nH + a.nKV ? 1 : 2);
-    if (kind != 0 && !a.write_kv) return;
-    const __nv_bfloat16* src = (const __nv_bfloat16*)a.qkv + ((size_t)t * heads + j) * a.hd;
-    uint4 raw = *(const uint4*)(src + c * 8);
-    float v[8];
-    {
-        const __nv_bfloat162* p2 = (const __nv_bfloat162*)&raw;
+    const unsigned chunks = a.hd >> 3, heads = a.nH + 2 * a.nKV;
+    const unsigned hc = a.half >> 3;                          // chunks in one half of the rotary part
+    const int t = blockIdx.x;
+    const unsigned n = (a.write_kv ? heads : (unsigned)a.nH) * chunks;
+    const __nv_bfloat16* row = (const __nv_bfloat16*)a.qkv + (size_t)t * heads * a.hd;
+    const float* cs_row = a.cosv ? a.cosv + (size_t)t * a.half : nullptr;
+    const float* sn_row = a.sinv ? a.sinv + (size_t)t * a.half : nullptr;
+    const int pos = a.tok_pos[t];
+    const size_t cache_row = a.write_kv
+        ? ((size_t)a.pages[(size_t)a.tok_seq[t] * a.max_pages + pos / GL_PAGE] * a.nKV * GL_PAGE + (pos % GL_PAGE)) * a.hd : 0;
+    for (unsigned i = threadIdx.x; i < n; i += blockDim.x) {
+        const unsigned j = i / chunks, c = i - j * chunks;
+        const int kind = j < (unsigned)a.nH ? 0 : (j < (unsigned)(a.nH + a.nKV) ? 1 : 2);
+        const __nv_bfloat16* src = row + (size_t)j * a.hd;
+        const uint4 raw = *(const uint4*)(src + c * 8);
+        float v[8];
+        {
+            const __nv_bfloat162* p2 = (const __nv_bfloat162*)&raw;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
-    }
-    const int hc = a.half >> 3;                               // chunks in one half of the rotary part
-    if (kind != 2 && a.cosv && c < 2 * hc) {
-        const bool low = c < hc;                                 // this chunk holds u (first half) or w (second half)
-        const uint4 praw = *(const uint4*)(src + (low ? c + hc : c - hc) * 8);
-        const __nv_bfloat162* q2 = (const __nv_bfloat162*)&praw;
-        const float* cs = a.cosv + (size_t)t * a.half + (low ? c : c - hc) * 8;
-        const float* sn = a.sinv + (size_t)t * a.half + (low ? c : c - hc) * 8;
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(p2[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+        }
+        if (kind != 2 && cs_row && c < 2 * hc) {
+            const bool low = c < hc;                             // this chunk holds u (first half) or w (second half)
+            const uint4 praw = *(const uint4*)(src + (low ? c + hc : c - hc) * 8);
+            const __nv_bfloat162* q2 = (const __nv_bfloat162*)&praw;
+            const float* cs = cs_row + (low ? c : c - hc) * 8;
+            const float* sn = sn_row + (low ? c : c - hc) * 8;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(q2[e]);
-            const float pw[2] = {f.x, f.y};
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(q2[e]);
+                const float pw[2] = {f.x, f.y};
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const float co = cs[2 * e + k], si = sn[2 * e + k];
-                // u' = u cos - w sin ;  w' = u sin + w cos
-                v[2 * e + k] = low ? v[2 * e + k] * co - pw[k] * si : pw[k] * si + v[2 * e + k] * co;
+                for (int k = 0; k < 2; ++k) {
+                    const float co = cs[2 * e + k], si = sn[2 * e + k];
+                    // u' = u cos - w sin ;  w' = u sin + w cos
+                    v[2 * e + k] = low ? v[2 * e + k] * co - pw[k] * si : pw[k] * si + v[2 * e + k] * co;
+                }
             }
         }
-    }
-    const float sc = kind == 0 ? a.q_scale : 1.0f;
-    uint4 out;
-    {
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0] * sc, v[1] * sc), p1 = __floats2bfloat162_rn(v[2] * sc, v[3] * sc);
-        __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4] * sc, v[5] * sc), p3 = __floats2bfloat162_rn(v[6] * sc, v[7] * sc);
-        out.x = *(unsigned*)&p0; out.y = *(unsigned*)&p1; out.z = *(unsigned*)&p2; out.w = *(unsigned*)&p3;
-    }
-    if (kind == 0) {
-        *(uint4*)((__nv_bfloat16*)a.q_out + ((size_t)t * a.nH + j) * a.hd + c * 8) = out;
-    } else {
-        const int head = kind == 1 ? j - a.nH : j - a.nH - a.nKV;
-        const int pos = a.tok_pos[t];
-        const int page = a.pages[(size_t)a.tok_seq[t] * a.max_pages + pos / GL_PAGE];
-        __nv_bfloat16* base = (__nv_bfloat16*)(kind == 1 ? a.k_cache : a.v_cache);
-        *(uint4*)(base + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * a.hd + c * 8) = out;
+        const float sc = kind == 0 ? a.q_scale : 1.0f;
+        uint4 out;
+        {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0] * sc, v[1] * sc), p1 = __floats2bfloat162_rn(v[2] * sc, v[3] * sc);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4] * sc, v[5] * sc), p3 = __floats2bfloat162_rn(v[6] * sc, v[7] * sc);
+            out.x = *(unsigned*)&p0; out.y = *(unsigned*)&p1; out.z = *(unsigned*)&p2; out.w = *(unsigned*)&p3;
+        }
+        if (kind == 0) {
+            *(uint4*)((__nv_bfloat16*)a.q_out + ((size_t)t * a.nH + j) * a.hd + c * 8) = out;
+        } else {
+            const unsigned head = kind == 1 ? j - a.nH : j - a.nH - a.nKV;
+            __nv_bfloat16* base = (__nv_bfloat16*)(kind == 1 ? a.k_cache : a.v_cache);
+            *(uint4*)(base + cache_row + (size_t)head * GL_PAGE * a.hd + c * 8) = out;
+        }
     }
 }
 
@@ -181,8 +186,7 @@ GL_API int gl_qkv_cache(const QkvCacheArgs* args, int act_dtype, int cache_dtype
     if (act_dtype == GL_BF16 && cache_dtype == GL_BF16 && !a.q_gamma && !a.k_gamma && !a.interleaved &&
         a.hd % 8 == 0 && a.half % 8 == 0 &&
         !(((uintptr_t)a.qkv | (uintptr_t)a.q_out | (uintptr_t)a.k_cache | (uintptr_t)a.v_cache) & 15)) {
-        const long long n = (long long)a.T * (a.nH + 2 * a.nKV) * (a.hd / 8);
-        return gl_launch(qkv_cache_bf16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
+        return gl_launch(qkv_cache_bf16_kernel, dim3((unsigned)a.T), dim3(256), 0, stream, 1, a);
     }
     const int warps = 4;
     const long long items = (long long)a.T * (a.nH + 2 * a.nKV);
