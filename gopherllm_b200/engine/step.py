@@ -81,7 +81,8 @@ class Engine:
         self.use_graphs = act_dtype == torch.bfloat16 and bool(getattr(model, "capturable", False))
         self.graph_max_batch = 256
         self.graph_first_runs = 2                            # runs of the schedule in a step's first, short graph
-        self._graphs: Dict[tuple, object] = {}
+        self._graphs: Dict[tuple, object] = {}             # insertion order = least recently used first
+        self.graph_limit = 64                                # captured steps kept (each holds its logits and descriptor)
         self._graph_pool = None
         self.overlap_branches = True                         # decode steps run parallel branches on two streams
         self._side_stream = None
@@ -286,9 +287,9 @@ class Engine:
         replay of the same shape."""
         bucket = self._length_bucket(max(meta["new_lens"]))
         key = lay.key() + (bucket,)
-        g = self._graphs.get(key)
+        g = self._graph_lookup(key)
         if g is None:
-            self._graphs[key] = False
+            self._graph_store(key, False)
             return None
         if g is False:
             g = _CapturedStep()
@@ -318,8 +319,20 @@ class Engine:
                 with torch.cuda.graph(g.graph, pool=self._graph_pool):
                     self.model.run(g.x, ctx, self.cache, n_first, n_runs)
                     g.logits = self.model.finish(g.x, ctx)
-            self._graphs[key] = g
+            self._graph_store(key, g)
         return g
+
+    def _graph_lookup(self, key):
+        g = self._graphs.get(key)
+        if g is not None:
+            self._graphs[key] = self._graphs.pop(key)        # most recently used last
+        return g
+
+    def _graph_store(self, key, g) -> None:
+        self._graphs.pop(key, None)
+        self._graphs[key] = g
+        while len(self._graphs) > self.graph_limit:          # the least recently used shape goes
+            del self._graphs[next(iter(self._graphs))]
 
     @torch.no_grad()
     def decode_loop(self, slots: Sequence[int], tokens: Sequence[int], steps: int, sampler) -> torch.Tensor:
@@ -338,7 +351,7 @@ class Engine:
         pin = self._stage(buf)
         bucket = self._length_bucket(max(ctxs) + steps)
         key = ("loop",) + lay.key() + (bucket,)
-        g = self._graphs.get(key)
+        g = self._graph_lookup(key)
         if g is None:
             g = _CapturedStep()
             g.desc = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
@@ -369,7 +382,7 @@ class Engine:
             with torch.cuda.graph(g.graph, pool=self._graph_pool):
                 body()
             self.launches_per_loop_step[B] = ops.LAUNCHES - before
-            self._graphs[key] = g
+            self._graph_store(key, g)
         if g.sampler is not sampler:
             raise ValueError("decode_loop was captured with another sampler for this batch size")
         if steps > g.history_cap:

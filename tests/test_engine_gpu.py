@@ -201,3 +201,40 @@ def test_batch_composition_does_not_change_a_row(dtype):
         assert np.array_equal(alone, out), "a 32-bit row changed with the batch around it"
     else:
         check(out, alone, dtype, "row in a batch vs alone")
+
+
+def test_captured_steps_are_kept_up_to_a_limit():
+    """Decode steps of the bfloat16 path replay a captured graph per batch size and length bucket; with
+    room for two, batches of 1, 2 and 3 in turn keep displacing one another, and every step's logits
+    still equal the plain implementation's."""
+    name = "B"
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(16)
+    m = model(name, "bfloat16")
+    eng = m.engine
+    old, kept = eng.graph_limit, dict(eng._graphs)
+    eng.graph_limit = 2
+    eng._graphs.clear()
+    try:
+        seqs = [tiny.prompt(rng, 40, cfg["vocab_size"]) for _ in range(3)]
+        refs = [plain_logits(name, t) for t in seqs]
+        slots = [m.open_sequence() for _ in seqs]
+        m.step([(s, t[:8]) for s, t in zip(slots, seqs)], [[], [], []])
+        fed = [8, 8, 8]
+        captured = 0
+        for rnd in range(18):
+            k = (rnd // 3) % 3 + 1                           # sequences 0..k-1 take one token; three steps a size
+            out = m.step([(slots[i], [seqs[i][fed[i]]]) for i in range(k)]).cpu().numpy()
+            for i in range(k):
+                err, bound = tiny.close(out[i], refs[i][fed[i]], "bfloat16")
+                assert err <= bound, (rnd, i, err)
+                fed[i] += 1
+            assert len(eng._graphs) <= 2
+            captured += sum(1 for g in eng._graphs.values() if g is not False)
+        assert captured > 0, "no step was replayed from a captured graph"
+        for s in slots:
+            m.close_sequence(s)
+    finally:
+        eng.graph_limit = old
+        eng._graphs.update(kept)
+    eng.cache.check()
