@@ -85,3 +85,25 @@ def test_cli_options():
     assert (s.temperature, s.top_k, s.top_p, s.repeat_penalty) == (0.5, 3, 0.9, 1.05) and a.max_tokens == 7
     a = build_parser().parse_args(["m"])
     assert effective_sampler(a) == SamplerConfig() and a.max_tokens == 256 and a.bench_runs == 3
+
+
+def test_decode_attention_splits_stay_within_the_machine():
+    """How decode attention is cut over blocks is a launch decision made on the host: never more blocks
+    than are resident at once, never more splits than pages or than a cluster holds, at least one."""
+    from unittest import mock
+    from gopherllm_b200 import ops
+    with mock.patch.object(ops, "sm_count", lambda device: 148):
+        for heads, hd in ((32, 80), (8, 128), (5, 32), (1, 256)):
+            slots = 148 * ops.decode_blocks_per_sm(hd, 1)
+            for batch in (1, 2, 3, 4, 7, 8, 16, 64, 300):
+                last = 0
+                for length in (1, 64, 65, 500, 1024, 2048, 8192, 100000):
+                    s = ops.decode_splits(batch, heads, length, "cuda:0", hd, 1)
+                    pages = -(-length // 64)
+                    assert 1 <= s <= min(8, pages)
+                    assert s == 1 or batch * heads * s <= slots
+                    assert s >= last                      # a longer sequence is never cut into fewer parts
+                    last = s
+        # Phi-2 shapes: the measured best cuts
+        assert [ops.decode_splits(b, 32, 2048, "cuda:0", 80, 1) for b in (1, 2, 4, 8, 16)] == [8, 4, 4, 2, 1]
+        assert [ops.decode_splits(b, 32, 512, "cuda:0", 80, 1) for b in (2, 4, 8)] == [4, 2, 1]
