@@ -79,8 +79,9 @@ class Model:
     def generate(self, prompts, **options):
         """Generate for one prompt (a list of token ids) or several (a list of
         lists).  Options: max_tokens, temperature, top_p, top_k, min_p,
-        repeat_penalty, seed, stop_tokens, should_stop.  Returns a
-        GenerationResult, or a list of them."""
+        repeat_penalty, seed, stop_tokens, should_stop, on_token (called with
+        (request index, token) for every token as it is emitted; returning
+        False cancels).  Returns a GenerationResult, or a list of them."""
         from .engine.generate import GenerationOptions, generate
         single = len(prompts) > 0 and not isinstance(prompts[0], (list, tuple))
         opts = options.pop("options", None) or GenerationOptions.from_kwargs(self.spec, **options)

@@ -203,6 +203,13 @@ def main(argv=None) -> int:
             print(json.dumps(rows))
         return 0
 
+    if len(prompts) == 1:
+        # one request: its tokens are printed as they come, as the reference streams its text
+        opts["on_token"] = lambda i, tok: print(tok, end=" ", flush=True)
+        r = one_run()[0]
+        print()
+        print(f"finish={r.finish_reason} {stats_line(r.stats)}", file=sys.stderr)
+        return 0
     for r in one_run():
         print(" ".join(map(str, r.tokens)))
         print(f"finish={r.finish_reason} {stats_line(r.stats)}", file=sys.stderr)

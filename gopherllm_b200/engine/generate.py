@@ -26,12 +26,16 @@ class GenerationOptions:
     max_tokens (default 256), sampler, seed (0: taken from the clock,
     runtime.go:906-910), stop_tokens (default: the model's end-of-sequence id,
     runtime.go:1914), should_stop (polled between steps, as the reference polls
-    its context, runtime.go:1131)."""
+    its context, runtime.go:1131), on_token(request index, token): called for every
+    emitted token as it is known; returning False cancels the generation with what
+    was generated so far (the reference's streaming callback, runtime.go:793-815,
+    1024, which gets text; this library is token-level)."""
     max_tokens: int = 256
     sampler: SamplerConfig = field(default_factory=SamplerConfig)
     seed: int = 0
     stop_tokens: Tuple[int, ...] = ()
     should_stop: Optional[Callable[[], bool]] = None
+    on_token: Optional[Callable[[int, int], Optional[bool]]] = None
 
     @classmethod
     def from_kwargs(cls, spec=None, **kw) -> "GenerationOptions":
@@ -45,7 +49,8 @@ class GenerationOptions:
         if stops is None:
             stops = tuple(spec.stop_tokens) if spec is not None else ()
         o = cls(max_tokens=kw.pop("max_tokens", 256), sampler=s, seed=kw.pop("seed", 0),
-                stop_tokens=tuple(int(t) for t in stops), should_stop=kw.pop("should_stop", None))
+                stop_tokens=tuple(int(t) for t in stops), should_stop=kw.pop("should_stop", None),
+                on_token=kw.pop("on_token", None))
         if kw:
             raise TypeError(f"unknown generation options: {', '.join(sorted(kw))}")
         return o
@@ -202,7 +207,12 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                 nxt, runs, kept = [], [], []
                 for i, (r, tok) in enumerate(zip(live, tokens)):
                     stats[r].token_times.append(now - t_start)
-                    if states[r].accept(tok):
+                    emitted = len(states[r].generated)
+                    goes_on = states[r].accept(tok)
+                    if options.on_token is not None and len(states[r].generated) > emitted:
+                        if options.on_token(batch[r], tok) is False:
+                            canceled = True
+                    if goes_on:
                         nxt.append(r)
                         runs.append((slots[r], [tok]))
                         kept.append(i)
@@ -214,7 +224,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                 if len(nxt) != len(live):
                     rows_dev = None
                 live = nxt
-                if options.should_stop is not None and options.should_stop():
+                if canceled or (options.should_stop is not None and options.should_stop()):
                     canceled = True
                     break
                 if runs:

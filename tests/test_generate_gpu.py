@@ -166,6 +166,34 @@ def test_cancel_between_steps():
     assert m.engine.cache.slots.held_count == 0
 
 
+def test_tokens_are_handed_out_as_they_come():
+    """on_token gets (request index, token) for every emitted token, in order per request, the stop
+    token never; returning False cancels with what was generated so far."""
+    import gopherllm_b200 as gl
+    name = "A"
+    cfg = tiny.TINY[name][0]
+    rng = np.random.default_rng(36)
+    prompts = [tiny.prompt(rng, n, cfg["vocab_size"]) for n in (6, 19, 3)]
+    m = model(name, "float32")
+    alone = m.generate(prompts[1], max_tokens=10, stop_tokens=(), **GREEDY).tokens
+    stop = alone[4]
+    seen = {0: [], 1: [], 2: []}
+    res = m.generate(prompts, max_tokens=10, stop_tokens=(stop,), on_token=lambda i, t: seen[i].append(t), **GREEDY)
+    for i, r in enumerate(res):
+        assert seen[i] == r.tokens and stop not in seen[i]
+    assert res[1].finish_reason == "stop" and len(res[1].tokens) <= 4
+    got = []
+
+    def three(i, t):
+        got.append(t)
+        return len(got) < 3
+    with pytest.raises(gl.GenerationCanceled) as e:
+        m.generate(prompts[0], max_tokens=10, stop_tokens=(), on_token=three, **GREEDY)
+    assert e.value.results[0].tokens == got and len(got) == 3 and e.value.results[0].finish_reason == "canceled"
+    m.engine.cache.check()
+    assert m.engine.cache.slots.held_count == 0
+
+
 def test_command_line():
     folder = tiny.folder("A")
     run = lambda *a: subprocess.run([sys.executable, "-m", "gopherllm_b200", folder, *a], cwd=ROOT,
