@@ -55,16 +55,18 @@ def parse_duration(text: str) -> float:
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="gopherllm_b200", description="Phi on one B200: generate, bench, inspect.")
-    ap.add_argument("model", help="model folder (config.json + model.safetensors)")
+    ap.add_argument("model", nargs="?", default=None,
+                    help="model folder (config.json + model.safetensors); may come from --config instead")
+    ap.add_argument("--config", dest="config_file", help="JSON file of options (version, preset, model, generation, runtime)")
     ap.add_argument("--prompt", "-p", help='token ids, e.g. "5 17 3"; ";" separates several prompts')
     ap.add_argument("--prompt-file", help="file with token ids, one prompt per line")
-    ap.add_argument("--max-tokens", "-n", type=int, default=256, help="max tokens to generate (default: 256)")
+    ap.add_argument("--max-tokens", "-n", type=int, default=None, help="max tokens to generate (default: 256)")
     ap.add_argument("--temp", "-t", type=float, default=None, help="temperature (default: 0.7, 0=greedy)")
     ap.add_argument("--top-p", type=float, default=None, help="nucleus sampling threshold (default: 0.9)")
     ap.add_argument("--top-k", type=int, default=None, help="top-K filtering (default: 40)")
     ap.add_argument("--min-p", type=float, default=None, help="min-P sampling threshold (default: 0, disabled)")
     ap.add_argument("--repeat-penalty", type=float, default=None, help="repetition penalty (default: 1.1)")
-    ap.add_argument("--seed", type=int, default=0, help="RNG seed (default: time-based)")
+    ap.add_argument("--seed", type=int, default=None, help="RNG seed (default: time-based)")
     ap.add_argument("--preset", choices=sorted(PRESETS), help="generation preset")
     ap.add_argument("--stop", action="append", default=None,
                     help="stop when this token id is sampled (repeatable; default: the model's eos_token_id)")
@@ -89,9 +91,78 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
-def effective_sampler(args) -> SamplerConfig:
-    base = PRESETS[args.preset] if args.preset else SamplerConfig()
+CONFIG_VERSION = 1
+# keys of the reference's options file (cmd/gopherllm/config.go:25-78); the ones this library has a use for
+_FILE_KEYS = {"version", "preset", "model", "generation", "runtime"}
+_FILE_GENERATION = {"max_tokens", "temperature", "top_p", "top_k", "min_p", "repeat_penalty", "seed", "stop"}
+_FILE_RUNTIME = {"timeout"}
+# and the ones it reads past (servers, model downloads, chat templates, CPU and Metal switches)
+_FILE_IGNORED = {"model_dir", "server", "huggingface"}
+_FILE_GENERATION_IGNORED = {"mtp_draft_tokens", "system_prompt", "context_window_mode"}
+_FILE_RUNTIME_IGNORED = {"threads", "metal", "prepare_quant", "out_of_core", "auto_tune", "auto_refresh", "auto_effort"}
+
+
+def load_file_config(path: str) -> dict:
+    """The options file of --config: one JSON object, unknown keys refused, version 0 or 1
+    (loadFileConfig, cmd/gopherllm/config.go:154-184)."""
+    try:
+        with open(path, "r", encoding="utf-8") as f:
+            raw = json.load(f)
+    except OSError as e:
+        raise SystemExit(f"open config {path}: {e}")
+    except json.JSONDecodeError as e:
+        raise SystemExit(f"decode config {path}: {e}")
+    if not isinstance(raw, dict):
+        raise SystemExit(f"decode config {path}: expected one JSON object")
+
+    def known(obj, allowed, ignored, where):
+        if not isinstance(obj, dict):
+            raise SystemExit(f"decode config {path}: {where} must be an object")
+        extra = sorted(set(obj) - allowed - ignored)
+        if extra:
+            raise SystemExit(f"decode config {path}: unknown field {where + '.' if where else ''}{extra[0]}")
+    known(raw, _FILE_KEYS, _FILE_IGNORED, "")
+    known(raw.get("generation") or {}, _FILE_GENERATION, _FILE_GENERATION_IGNORED, "generation")
+    known(raw.get("runtime") or {}, _FILE_RUNTIME, _FILE_RUNTIME_IGNORED, "runtime")
+    if raw.get("version", 0) not in (0, CONFIG_VERSION):
+        raise SystemExit(f"config {path} has unsupported version {raw['version']} (supported: {CONFIG_VERSION})")
+    if raw.get("preset") and str(raw["preset"]).strip().lower() not in PRESETS:
+        raise SystemExit("config preset: preset must be balanced, precise, creative, or deterministic")
+    return raw
+
+
+def apply_file_config(args, raw: dict) -> None:
+    """What the file sets and no flag does: the order is defaults, the file's preset, the file's values,
+    --preset, then the other flags (cmd/gopherllm/main.go:686-707, config.go:186-260)."""
+    gen, run = raw.get("generation") or {}, raw.get("runtime") or {}
+    if args.model is None and raw.get("model"):
+        args.model = raw["model"]
+    if args.max_tokens is None and gen.get("max_tokens") is not None:
+        args.max_tokens = int(gen["max_tokens"])
+    if args.seed is None and gen.get("seed") is not None:
+        args.seed = int(gen["seed"])
+    if args.stop is None and gen.get("stop") is not None:
+        args.stop = [str(t) for t in gen["stop"]]
+    if args.timeout is None and run.get("timeout") is not None:
+        if parse_duration(str(run["timeout"])) <= 0:
+            raise SystemExit("config runtime.timeout must be a duration greater than 0")
+        args.timeout = str(run["timeout"])
+
+
+def effective_sampler(args, file_config: dict = None) -> SamplerConfig:
+    base = SamplerConfig()
     s = SamplerConfig(base.temperature, base.top_p, base.top_k, base.min_p, base.repeat_penalty)
+    if file_config:
+        if file_config.get("preset"):
+            p = PRESETS[str(file_config["preset"]).strip().lower()]
+            s = SamplerConfig(p.temperature, p.top_p, p.top_k, p.min_p, p.repeat_penalty)
+        gen = file_config.get("generation") or {}
+        for field in ("temperature", "top_p", "top_k", "min_p", "repeat_penalty"):
+            if gen.get(field) is not None:
+                setattr(s, field, int(gen[field]) if field == "top_k" else float(gen[field]))
+    if args.preset:
+        p = PRESETS[args.preset]
+        s = SamplerConfig(p.temperature, p.top_p, p.top_k, p.min_p, p.repeat_penalty)
     for field, value in (("temperature", args.temp), ("top_p", args.top_p), ("top_k", args.top_k),
                          ("min_p", args.min_p), ("repeat_penalty", args.repeat_penalty)):
         if value is not None:
@@ -131,6 +202,13 @@ def stats_line(s) -> str:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
+    file_config = load_file_config(args.config_file) if args.config_file else None
+    if file_config:
+        apply_file_config(args, file_config)
+    if args.model is None:
+        raise SystemExit("give a model folder (or \"model\" in the --config file)")
+    args.max_tokens = 256 if args.max_tokens is None else args.max_tokens
+    args.seed = 0 if args.seed is None else args.seed
     if args.random_config:
         from .api import write_random_model
         with open(args.random_config) as f:
@@ -139,10 +217,10 @@ def main(argv=None) -> int:
         return 0
     if args.inspect or args.list_tensors or args.list_metadata:
         return inspect(args.model, args.list_metadata, args.list_tensors)
-    sampler = effective_sampler(args)
+    sampler = effective_sampler(args, file_config)
     if args.print_config:
         print(json.dumps({"model": args.model, "dtype": args.dtype, "max_tokens": args.max_tokens,
-                          "seed": args.seed, "preset": args.preset, "sampler": vars(sampler),
+                          "seed": args.seed, "preset": args.preset or (file_config or {}).get("preset"), "sampler": vars(sampler),
                           "stop": args.stop, "timeout": args.timeout}, indent=2))
         return 0
 

@@ -84,7 +84,40 @@ def test_cli_options():
     s = effective_sampler(a)
     assert (s.temperature, s.top_k, s.top_p, s.repeat_penalty) == (0.5, 3, 0.9, 1.05) and a.max_tokens == 7
     a = build_parser().parse_args(["m"])
-    assert effective_sampler(a) == SamplerConfig() and a.max_tokens == 256 and a.bench_runs == 3
+    assert effective_sampler(a) == SamplerConfig() and a.max_tokens is None and a.bench_runs == 3
+
+
+def test_options_file(tmp_path, capsys):
+    """--config: defaults, then the file's preset, the file's values, --preset, the other flags
+    (cmd/gopherllm/main.go:686-707); unknown keys and versions are refused, the reference's keys that
+    this library has no use for are read past."""
+    import json
+    from gopherllm_b200.cli import main
+    f = tmp_path / "options.json"
+    f.write_text(json.dumps({"version": 1, "preset": "precise", "model": "some/folder",
+                             "generation": {"max_tokens": 33, "temperature": 0.4, "seed": 9, "stop": ["7", "8"],
+                                            "system_prompt": "unused here"},
+                             "runtime": {"timeout": "2m", "threads": 4}, "server": {"address": ":1"}}))
+
+    def shown(*argv):
+        assert main(list(argv) + ["--print-config"]) == 0
+        return json.loads(capsys.readouterr().out)
+    c = shown("--config", str(f))
+    assert c["model"] == "some/folder" and c["max_tokens"] == 33 and c["seed"] == 9 and c["stop"] == ["7", "8"]
+    assert c["timeout"] == "2m" and c["preset"] == "precise"
+    assert c["sampler"] == dict(temperature=0.4, top_p=0.9, top_k=30, min_p=0.0, repeat_penalty=1.05)
+    c = shown("other", "--config", str(f), "-n", "5", "--top-k", "2", "--seed", "4")      # flags win over the file
+    assert c["model"] == "other" and c["max_tokens"] == 5 and c["seed"] == 4 and c["sampler"]["top_k"] == 2
+    assert c["sampler"]["temperature"] == 0.4
+    c = shown("--config", str(f), "--preset", "creative")                               # --preset resets the sampler
+    assert c["sampler"] == dict(temperature=0.95, top_p=0.95, top_k=80, min_p=0.05, repeat_penalty=1.05)
+    for bad in ({"version": 2}, {"generation": {"tempo": 1}}, {"colour": "red"}, {"preset": "wild"},
+                {"runtime": {"timeout": "never"}}, [1, 2]):
+        f.write_text(json.dumps(bad))
+        with pytest.raises(SystemExit):
+            main(["m", "--config", str(f), "--print-config"])
+    with pytest.raises(SystemExit):
+        main(["--print-config"])                                                        # no model anywhere
 
 
 def test_decode_attention_splits_stay_within_the_machine():
