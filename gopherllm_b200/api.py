@@ -16,7 +16,7 @@ from typing import Callable, List, Optional, Sequence
 import torch
 
 from .cache.sequence_cache import SequenceCache
-from .config import load_config
+from .config import load_config, read_config_json
 from .config.registry import Architecture
 from .engine.model import DecoderModel
 from .engine.step import Engine
@@ -102,13 +102,20 @@ def build_model(arch: Architecture, config) -> DecoderModel:
 
 
 def load(path: str, dtype="bfloat16", max_tokens: Optional[int] = None, device="cuda:0",
-         max_slots: Optional[int] = None, log: Optional[Callable[[str], None]] = None) -> Model:
+         max_slots: Optional[int] = None, log: Optional[Callable[[str], None]] = None,
+         keep_stored: Optional[bool] = None) -> Model:
     """Open a model folder (config.json + model.safetensors).
 
     dtype: "bfloat16" (the serving kernels) or "float32" (everything in true
     32-bit).  max_tokens: positions the cache holds for all live sequences
     together, each rounded up to 64 (default: 8 sequences of the model's full
     length).  Silent unless ``log`` is given (the reference: api.go:44-54).
+    With dtype "bfloat16", matrices stored in another type (float16 as in the
+    published Phi checkpoints, or a checkpoint that is 32-bit as a whole) are rounded
+    to bfloat16 when loading, and ``log`` is told so; a matrix stored in 32-bit
+    inside a 16-bit checkpoint stays 32-bit.  keep_stored=True keeps every matrix
+    that is not stored as bfloat16 in 32-bit (exact, and slow: such products run on
+    CUDA cores); keep_stored=False rounds every matrix.
     """
     device = _require_cuda(device)
     cdt = compute_dtype(dtype)
@@ -120,7 +127,10 @@ def load(path: str, dtype="bfloat16", max_tokens: Optional[int] = None, device="
     ignore = ("lm_head.weight",) if model.spec.tie_embeddings else ()
     fused = names.fused() if hasattr(names, "fused") else None
     with torch.cuda.device(device):
-        tensors, nbytes = load_folder(path, table, cdt, device, ignore=ignore, progress=log, fused=fused)
+        raw = read_config_json(path)       # the type the checkpoint declares, None if it declares none
+        declared = STORAGE_DTYPES.get(str(raw.get("torch_dtype", raw.get("dtype"))))
+        tensors, nbytes = load_folder(path, table, cdt, device, ignore=ignore, progress=log, fused=fused,
+                                      declared=declared, keep_stored=keep_stored)
         model.load(tensors)
         del tensors
         if max_tokens is None:
@@ -138,11 +148,18 @@ def load(path: str, dtype="bfloat16", max_tokens: Optional[int] = None, device="
     return Model(arch, config, engine, info)
 
 
+def _draw_workers() -> int:
+    return max(1, min(16, (os.cpu_count() or 1)))
+
+
 def load_random(config, seed: int = 0, dtype="bfloat16", max_tokens: Optional[int] = None,
                 device="cuda:0", max_slots: Optional[int] = None, layers: Optional[int] = None) -> Model:
-    """A model with seeded random weights built in memory: the tensors that
-    write_random_model(..., device=device) would write, without the folder.  ``layers``
-    keeps only the first so many layers (for machines or tests short of memory)."""
+    """A model with seeded random weights built in memory: tensor for tensor what
+    ``write_random_model(folder, config, seed)`` writes and ``load(folder, dtype)`` then holds (the
+    tensors are drawn on the CPU from the same per-tensor generators, several at a time, and rounded
+    by the same rule), without the folder.  ``layers`` keeps only the first so many layers (for
+    machines or tests short of memory): those layers, the embedding and the head are the same
+    tensors as in the full model, since each is drawn from (seed, its own name)."""
     from .config.registry import architecture_from_config
     from .weights.loader import random_tensors, resident_dtype
     device = _require_cuda(device)
@@ -159,9 +176,9 @@ def load_random(config, seed: int = 0, dtype="bfloat16", max_tokens: Optional[in
     sigma = float(getattr(cfg, "initializer_range", 0.02))
     tensors = {}
     with torch.cuda.device(device):
-        for name, t in random_tensors(table, seed, sigma, storage, device, to_cpu=False):
+        for name, t in random_tensors(table, seed, sigma, storage, workers=_draw_workers()):
             key, spec = table[name]
-            tensors[key] = t.to(resident_dtype(spec, storage, cdt)).contiguous()
+            tensors[key] = t.to(device).to(resident_dtype(spec, storage, cdt, storage)).contiguous()
         model.load(tensors)
         del tensors
         if max_tokens is None:
@@ -176,7 +193,7 @@ def load_random(config, seed: int = 0, dtype="bfloat16", max_tokens: Optional[in
     return Model(arch, cfg, engine, info)
 
 
-def write_random_model(folder: str, config, seed: int = 0, device="cpu") -> None:
+def write_random_model(folder: str, config, seed: int = 0) -> None:
     """Write config.json and model.safetensors of a model with seeded random
     weights.  ``config`` is a config.json dict or a typed configuration.  Matrices
     are N(0, initializer_range), stored in the config's torch_dtype."""
@@ -188,4 +205,4 @@ def write_random_model(folder: str, config, seed: int = 0, device="cpu") -> None
     table = tensor_table(model.parameters(), arch.tensor_names(cfg))
     storage = STORAGE_DTYPES.get(str(getattr(cfg, "torch_dtype", "bfloat16")), torch.bfloat16)
     write_model_folder(folder, cfg.to_dict(), table, seed, float(getattr(cfg, "initializer_range", 0.02)),
-                       storage, device)
+                       storage, workers=_draw_workers())

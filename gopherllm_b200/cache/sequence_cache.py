@@ -131,6 +131,24 @@ class SequenceCache:
                 s[slot].zero_()
         return slot
 
+    def state_snapshot(self, slots: Sequence[int]) -> List[torch.Tensor]:
+        """Copies of these sequences' rows of every state tensor (the reference saves and restores
+        such state around work that must leave no trace, qwen35.go:306-322)."""
+        states = [s for s in self._states if s is not None]
+        if not states:
+            return []
+        idx = torch.tensor([int(s) for s in slots], dtype=torch.int64).to(self.device)
+        return [s.index_select(0, idx) for s in states]
+
+    def state_restore(self, slots: Sequence[int], rows: Sequence[torch.Tensor]) -> None:
+        """Put back what ``state_snapshot`` took for the same sequences."""
+        states = [s for s in self._states if s is not None]
+        if not states:
+            return
+        idx = torch.tensor([int(s) for s in slots], dtype=torch.int64).to(self.device)
+        for s, r in zip(states, rows):
+            s.index_copy_(0, idx, r)
+
     def length(self, slot: int) -> int:
         self._held(slot)
         return self._length[slot]

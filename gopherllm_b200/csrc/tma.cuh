@@ -106,6 +106,19 @@ static int gl_cached_map_bf16(CUtensorMap* out, const void* base, uint64_t rows,
 // A wait that ran out sets this word; launchers expose it to the host.
 __device__ int gl_wait_failed = 0;
 
+// The word as the host sees it: 1 if a bounded wait of this library ran out since the word was last
+// cleared (what that launch computed, and everything computed from it, is invalid), -1 if the word
+// could not be read.  ``clear`` sets it back to 0 once read.  The copy waits for the device.
+GL_API int gl_wait_status(int clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, gl_wait_failed, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0 && clear) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(gl_wait_failed, &zero, sizeof(int)) != cudaSuccess) return -1;
+    }
+    return v;
+}
+
 #define GL_SPIN_LIMIT (1u << 22)      // tries before a wait gives up (each try may itself sleep briefly)
 
 __device__ __forceinline__ unsigned gl_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }

@@ -162,6 +162,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                            cache.n_pages, cache.max_slots)
     results: List[Optional[GenerationResult]] = [None] * len(prompts)
     prepare = getattr(engine, "prepare_decode", None)
+    # kernels that gave up a bounded wait leave a status word: read where the host waits anyway, so that
+    # an invalid result is an error here, as errors of the reference's forward pass end its loop
+    # (runtime.go:1131-1165), and not a wrong token
+    check = getattr(engine, "check_device", lambda: None)
     fetch = getattr(engine, "fetch", None) if prepare is not None else None
     for batch in batches:
         t_start = time.perf_counter()
@@ -199,6 +203,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                 tokens = fetch(chosen, sampled) if sampled is not None else chosen.tolist()   # waits for the sampling
                 now = time.perf_counter()
                 if first:
+                    check()                      # the prompts' step is over: the host has its tokens
                     t_prefill_end = now
                     for r in live:
                         stats[r].prefill_time = now - t_start
@@ -235,6 +240,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], options: GenerationOption
                         logits = engine.finish_decode(ahead, tokens)
                     else:
                         logits = engine.step(runs)
+            check()                              # the batch is over and the host has waited for its last tokens
         finally:
             for s in slots:
                 if s is not None:

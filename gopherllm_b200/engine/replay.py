@@ -28,6 +28,7 @@ def run(model, lines, out_dir: str, emit=print) -> None:
     """Replay ``lines`` (an iterable of JSON strings) on a loaded Model."""
     os.makedirs(out_dir, exist_ok=True)
     slots: Dict[str, int] = {}
+    check = getattr(getattr(model, "engine", None), "check_device", lambda: None)
     for line in lines:
         line = line.strip()
         if not line:
@@ -45,6 +46,7 @@ def run(model, lines, out_dir: str, emit=print) -> None:
             logits = model.step(runs, want)
             if logits.shape[0] > 0:
                 arr = logits.detach().float().cpu().numpy().astype("<f4", copy=False)
+                check()                          # the copy waited for the step: a kernel that gave up is an error
                 arr.tofile(os.path.join(out_dir, f"{step}.f32"))
         for rid in rec.get("end", []):
             rid = str(rid)

@@ -93,6 +93,7 @@ class Engine:
         self._events: List[Optional[torch.cuda.Event]] = [None, None]
         self._flip = 0
         self.h2d_bytes_last = 0
+        self._logits_aliased = False                         # the last launch returned a captured graph's buffer
 
     # -- sequences ----------------------------------------------------------
     def open(self) -> int:
@@ -100,6 +101,14 @@ class Engine:
 
     def close(self, slot: int) -> None:
         self.cache.close(slot)
+
+    def check_device(self) -> None:
+        """Raise KernelError if a kernel gave up a bounded wait since the last check (its results, and
+        everything computed from them, are invalid).  Reading the status words synchronises with the
+        device, so callers do it where they wait for the device anyway: after a step whose results they
+        copy to the host, at the end of a batch."""
+        from .. import ops
+        ops.check_wait_failures()
 
     # -- the step -------------------------------------------------------------
     def plan(self, runs: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]]):
@@ -128,6 +137,10 @@ class Engine:
                     raise ValueError(f"wanted place {i} is outside a run of {q} tokens")
                 rows.append(start + int(i))
             start += q
+        toks = np.concatenate([np.asarray(t, dtype=np.int64) for _, t in runs])
+        if toks.min() < 0 or toks.max() >= self.vocab:
+            raise ValueError(f"token id outside [0, {self.vocab})")
+        # every check that can refuse the step comes before this line: a refused step holds nothing
         cache.reserve([(s, c + q) for s, c, q in zip(slots, ctxs, qlens)])
         lay = _Layout(T, B, len(rows), len(cache.groups), cache.max_pages_per_seq)
         buf = np.zeros(lay.size, dtype=np.int32)
@@ -136,9 +149,6 @@ class Engine:
             o, n = lay.off[name]
             buf[o:o + n] = values
 
-        toks = np.concatenate([np.asarray(t, dtype=np.int64) for _, t in runs])
-        if toks.min() < 0 or toks.max() >= self.vocab:
-            raise ValueError(f"token id outside [0, {self.vocab})")
         put("tokens", toks)
         put("tok_seq", np.repeat(np.arange(B), qlens))
         put("tok_pos", np.concatenate([np.arange(c, c + q) for c, q in zip(ctxs, qlens)]))
@@ -199,7 +209,10 @@ class Engine:
         (default: the last token of every run).  Returns float32 [wanted, vocab] on
         the device, in the order of runs and of want."""
         lay, buf, meta = self.plan(runs, want)
-        return self._launch(lay, self._stage(buf), meta)
+        logits = self._launch(lay, self._stage(buf), meta)
+        # a replayed step leaves its logits in the captured graph's own buffer, which the next step of
+        # the same shape overwrites: the caller gets a tensor that stays as it is
+        return logits.clone() if self._logits_aliased else logits
 
     def prepare_decode(self, slots: Sequence[int]):
         """The host's share of a one-token step that does not depend on the tokens themselves:
@@ -212,7 +225,9 @@ class Engine:
     def finish_decode(self, handle, tokens) -> torch.Tensor:
         """Launch a prepared one-token step.  ``tokens``: one id per sequence from the host, or an
         int32 tensor on the device (a sampler's output): the step then reads its tokens where the
-        sampler left them, so it can be launched before the host has seen them."""
+        sampler left them, so it can be launched before the host has seen them.  The logits of a
+        replayed step are the captured graph's own buffer: they hold until the next step of the same
+        shape (``step`` hands out a copy instead)."""
         lay, pin, meta = handle
         o, n = lay.off["tokens"]
         if isinstance(tokens, torch.Tensor):
@@ -247,6 +262,7 @@ class Engine:
     def _launch(self, lay: _Layout, pin: torch.Tensor, meta: dict,
                 tokens_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
         graph = None
+        self._logits_aliased = False
         if self.use_graphs and meta["is_decode"] and lay.B <= self.graph_max_batch:
             graph = self._decode_graph(lay, meta)
         o, n = lay.off["tokens"]
@@ -259,6 +275,7 @@ class Engine:
             if graph.graph is not None:
                 graph.graph.replay()
             logits = graph.logits
+            self._logits_aliased = True
         else:
             dev = torch.empty(lay.size, dtype=torch.int32, device=self.device)
             dev.copy_(pin, non_blocking=True)
@@ -296,7 +313,7 @@ class Engine:
             g.desc = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
             bound = dict(meta)
             bound["new_lens"] = [bucket]                        # launch sizes are chosen for the bucket's longest
-            ctx = self.context(lay, g.desc, bound)
+            ctx = g.ctx = self.context(lay, g.desc, bound)     # lives as long as the graphs: they read its tables
             torch.cuda.synchronize(self.device)
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
@@ -343,60 +360,77 @@ class Engine:
         from .. import ops
         if steps < 1:
             raise ValueError("steps must be at least 1")
+        history_cap = 4096
+        if steps > history_cap:
+            raise ValueError(f"decode_loop runs at most {history_cap} steps a call")
         cache = self.cache
         B = len(slots)
+        if len(tokens) != B or len(set(int(s) for s in slots)) != B:
+            raise ValueError("decode_loop takes one token for each of its distinct sequences")
+        if min(int(t) for t in tokens) < 0 or max(int(t) for t in tokens) >= self.vocab:
+            raise ValueError(f"token id outside [0, {self.vocab})")
         ctxs = [cache.length(s) for s in slots]
+        # pages for all steps first: the page table staged below then covers every position of the loop
         cache.reserve([(s, c + steps) for s, c in zip(slots, ctxs)])
         lay, buf, meta = self.plan([(s, [t]) for s, t in zip(slots, tokens)], None)
         pin = self._stage(buf)
         bucket = self._length_bucket(max(ctxs) + steps)
-        key = ("loop",) + lay.key() + (bucket,)
+        # a captured loop step has its sampler's options and state buffers as kernel arguments
+        key = ("loop", id(sampler)) + lay.key() + (bucket,)
         g = self._graph_lookup(key)
         if g is None:
             g = _CapturedStep()
             g.desc = torch.zeros(lay.size, dtype=torch.int32, device=self.device)
             g.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-            g.history_cap = 4096
-            g.history = torch.zeros((g.history_cap, B), dtype=torch.int32, device=self.device)
+            g.history = torch.zeros((history_cap, B), dtype=torch.int32, device=self.device)
             g.state_row = torch.arange(B, dtype=torch.int32, device=self.device)
-            bound = dict(meta)
-            bound["new_lens"] = [bucket]
-            ctx = self.context(lay, g.desc, bound)
-
-            def body():
-                logits = self.model.forward(ctx, cache)
-                chosen = g.sampler.sample(logits, g.state_row)
-                ops.advance_decode(ctx.tokens, ctx.tok_pos, ctx.seq_ctx, chosen, g.history, g.counter)
-
             g.sampler = sampler
+            g.bound = dict(meta)
+            g.bound["new_lens"] = [bucket]                     # launch sizes are chosen for the bucket's longest
+
+        def body(ctx):
+            logits = self.model.forward(ctx, cache)
+            chosen = g.sampler.sample(logits, g.state_row)
+            ops.advance_decode(ctx.tokens, ctx.tok_pos, ctx.seq_ctx, chosen, g.history, g.counter)
+
+        if g.graph is None and getattr(self.model, "capturable", False):
             g.desc.copy_(pin, non_blocking=True)
+            # Once kernel by kernel, which loads and warms everything, with a context of its own: what
+            # the parts memoise per step (position tables) must be computed again inside the capture,
+            # or the graph would go on reading the warm-up step's tables at every position.  The
+            # warm-up leaves no trace: the sampler's state and the sequences' state rows are put back,
+            # and the keys and values it wrote are written again, equal, by the first replay.
             saved = [t.clone() for t in (sampler.rng, sampler.recent, sampler.recent_n)]
-            body()                                   # kernel by kernel once: loads and warms everything
+            states = cache.state_snapshot(slots)
+            body(self.context(lay, g.desc, g.bound))
             for t, keep in zip((sampler.rng, sampler.recent, sampler.recent_n), saved):
-                t.copy_(keep)                        # the warm-up step drew nothing as far as the caller sees
+                t.copy_(keep)
+            cache.state_restore(slots, states)
             torch.cuda.synchronize(self.device)
+            g.ctx = self.context(lay, g.desc, g.bound)        # fresh, and kept with the graph that reads its tables
             g.graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
             before = ops.LAUNCHES
             with torch.cuda.graph(g.graph, pool=self._graph_pool):
-                body()
+                body(g.ctx)
             self.launches_per_loop_step[B] = ops.LAUNCHES - before
-            self._graph_store(key, g)
-        if g.sampler is not sampler:
-            raise ValueError("decode_loop was captured with another sampler for this batch size")
-        if steps > g.history_cap:
-            raise ValueError(f"decode_loop runs at most {g.history_cap} steps a call")
+        self._graph_store(key, g)
         g.desc.copy_(pin, non_blocking=True)
         self._staged_done()
         g.counter.zero_()
-        for _ in range(steps):
-            g.graph.replay()
+        if g.graph is not None:
+            for _ in range(steps):
+                g.graph.replay()
+        else:                                                   # a model with a part that cannot be captured
+            for _ in range(steps):
+                body(self.context(lay, g.desc, g.bound))
         for s, c in zip(slots, ctxs):
             cache.commit(s, c + steps)
         return g.history[:steps]
 
 
 class _CapturedStep:
-    """A CUDA graph of one step with the buffers it reads and writes."""
-    desc = graph = logits = None
+    """A CUDA graph of one step with the buffers it reads and writes, and the step context it was
+    captured with (whose per-step memos, such as position tables, are nodes' outputs in the graph)."""
+    desc = graph = logits = ctx = bound = None

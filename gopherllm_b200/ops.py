@@ -564,15 +564,24 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     return out if fork is None else (out, out_b)
 
 
-def wait_failures() -> dict:
-    """Which libraries recorded a bounded wait that ran out (their last results are invalid)."""
+def wait_failures(clear: bool = False) -> dict:
+    """Which of the loaded libraries recorded a bounded wait that ran out (what they computed since is
+    invalid): library name -> 1, 0, or -1 if the word could not be read.  ``clear`` sets the words back
+    to 0.  Reading a word waits for the device."""
     out = {}
-    for src, fn in (("gemm_tcgen05.cu", "gl_gemm_tcgen05_wait_failed"), ("gemm_skinny.cu", "gl_gemm_skinny_wait_failed")):
-        out[src] = int(getattr(_lib(src), fn)())
     for key, lib in list(build._loaded.items()):
-        if "attention_prefill_tc" in key:
-            out[key] = int(lib.gl_attention_prefill_tc_wait_failed())
+        if hasattr(lib, "gl_wait_status"):
+            out[key] = int(lib.gl_wait_status(c_int(1 if clear else 0)))
     return out
+
+
+def check_wait_failures() -> None:
+    """Raise KernelError naming every library whose kernels gave up a bounded wait since the last
+    check; the words are cleared, so the next check speaks of what ran after this one."""
+    bad = sorted(k for k, v in wait_failures(clear=True).items() if v != 0)
+    if bad:
+        raise KernelError("a kernel gave up waiting (for a TMA copy or a tensor-core product) in "
+                          + ", ".join(bad) + ": the results since the last check are invalid")
 
 
 def linear_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],

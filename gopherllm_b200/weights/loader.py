@@ -60,16 +60,30 @@ def tensor_table(model_parameters: Dict[str, ParamSpec], names) -> Dict[str, Tup
     return table
 
 
-def resident_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype) -> torch.dtype:
-    """The type a tensor is held in.  Integer tables: int32.  1-D tensors:
-    float32 (model.go:2519-2528).  Matrices: float32 in the 32-bit path; in the
-    bfloat16 path a matrix stored in bfloat16 stays so, one stored in 32-bit
-    stays 32-bit, other types widen to float32."""
+_WIDE = (torch.float32, torch.float64)
+_HALF = (torch.bfloat16, torch.float16)
+
+
+def resident_dtype(spec: ParamSpec, stored: torch.dtype, compute: torch.dtype,
+                   declared: Optional[torch.dtype] = None, keep_stored: Optional[bool] = None) -> torch.dtype:
+    """The type a tensor is held in.  Integer tables: int32.  1-D tensors: float32
+    (model.go:2519-2528).  Matrices: float32 in the 32-bit path.  In the bfloat16 path every stored
+    type is brought to the compute type when loading, as the reference expands F32, F16, BF16 and F64
+    alike to its compute type (model.go:2399-2436): a matrix stored as float16 (the published Phi
+    checkpoints) is rounded to bfloat16, nearest even, and so is a checkpoint that is 32-bit as a whole
+    (``declared``, the folder's torch_dtype, is 32-bit or unknown).  One exception: a matrix stored in
+    32-bit inside a checkpoint that declares a 16-bit type was stored wider on purpose and stays
+    float32 (its products then run on the 32-bit CUDA-core kernel).  ``keep_stored`` True keeps every
+    matrix that is not stored as bfloat16 in float32 instead; False rounds all of them."""
     if spec.kind == "table_int":
         return torch.int32
     if spec.kind == "vector" or compute == torch.float32:
         return torch.float32
-    return torch.bfloat16 if stored == torch.bfloat16 else torch.float32
+    if stored == torch.bfloat16:
+        return torch.bfloat16
+    if keep_stored is None:
+        keep_stored = stored in _WIDE and declared in _HALF
+    return torch.float32 if keep_stored else torch.bfloat16
 
 
 def split_fused(entries: Dict[str, TensorEntry], table: Dict[str, Tuple[str, ParamSpec]],
@@ -126,11 +140,14 @@ def check_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], ignore: T
 
 def load_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], compute: torch.dtype, device,
                 ignore: Tuple[str, ...] = (), progress: Optional[Callable[[str], None]] = None,
-                fused: Optional[Dict[str, List[str]]] = None) -> Tuple[Dict[str, torch.Tensor], int]:
-    """Tensors by model parameter key, on ``device``; and the bytes read."""
+                fused: Optional[Dict[str, List[str]]] = None, declared: Optional[torch.dtype] = None,
+                keep_stored: Optional[bool] = None) -> Tuple[Dict[str, torch.Tensor], int]:
+    """Tensors by model parameter key, on ``device``, in their resident types (``resident_dtype``);
+    and the bytes read.  Tensors are copied as stored and rounded on the device."""
     entries = check_folder(folder, table, ignore, fused)
     out: Dict[str, torch.Tensor] = {}
     nbytes = 0
+    rounded: Dict[str, int] = {}
     with TensorFile(entries) as tf:
         for i, (name, (key, spec)) in enumerate(sorted(table.items())):
             if name not in entries:          # optional and absent
@@ -138,9 +155,16 @@ def load_folder(folder: str, table: Dict[str, Tuple[str, ParamSpec]], compute: t
                 continue
             t = tf.get(name)
             nbytes += t.numel() * t.element_size()
-            out[key] = t.to(device=device, dtype=resident_dtype(spec, t.dtype, compute)).contiguous()
+            want = resident_dtype(spec, t.dtype, compute, declared, keep_stored)
+            if spec.kind == "matrix" and want == torch.bfloat16 and t.dtype != torch.bfloat16:
+                label = str(t.dtype).replace("torch.", "")
+                rounded[label] = rounded.get(label, 0) + 1
+            out[key] = t.to(device=device).to(dtype=want).contiguous()
             if progress and i % 64 == 0:
                 progress(f"loaded {i + 1}/{len(table)} tensors")
+    if progress and rounded:
+        progress("rounded to bfloat16 (nearest even) at load: "
+                 + ", ".join(f"{n} matrices stored as {k}" for k, n in sorted(rounded.items())))
     return out, nbytes
 
 
@@ -152,40 +176,65 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
+def random_tensor(name: str, spec: ParamSpec, seed: int, sigma: float, storage: torch.dtype) -> torch.Tensor:
+    """One declared tensor of the random-weights mode, drawn on the CPU from a generator seeded by
+    (seed, name), in float32, and rounded to ``storage``."""
+    if spec.kind == "table_int":
+        return torch.zeros(spec.shape, dtype=torch.int32)
+    g = torch.Generator(device="cpu")
+    g.manual_seed(_tensor_seed(seed, name))
+    z = torch.randn(spec.shape, generator=g, dtype=torch.float32)
+    if spec.init == "normal":
+        t = z.mul_(sigma)
+    elif spec.init in ("bias", "beta"):
+        t = z.mul_(0.02)
+    elif spec.init == "gamma":
+        t = z.mul_(0.02).add_(1.0)
+    elif spec.init == "zeros":
+        t = z.zero_()
+    else:
+        raise ValueError(f"{name}: unknown initialisation {spec.init!r}")
+    return t.to(storage)
+
+
 def random_tensors(table: Dict[str, Tuple[str, ParamSpec]], seed: int, sigma: float,
-                   storage: torch.dtype, device="cpu", to_cpu: bool = True
-                   ) -> Iterator[Tuple[str, torch.Tensor]]:
-    """(name, tensor) for every declared tensor, each from a generator seeded by
-    (seed, name) so values do not depend on the order of generation.  Matrices
-    N(0, sigma); biases and norm offsets N(0, 0.02); norm scales 1 + N(0, 0.02).
-    Drawn in float32 on ``device`` and rounded to ``storage``."""
-    for name, (_, spec) in sorted(table.items()):
-        if spec.kind == "table_int":
-            yield name, torch.zeros(spec.shape, dtype=torch.int32)
-            continue
-        g = torch.Generator(device=device)
-        g.manual_seed(_tensor_seed(seed, name))
-        z = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
-        if spec.init == "normal":
-            t = z * sigma
-        elif spec.init in ("bias", "beta"):
-            t = z * 0.02
-        elif spec.init == "gamma":
-            t = 1.0 + z * 0.02
-        elif spec.init == "zeros":
-            t = torch.zeros_like(z)
-        else:
-            raise ValueError(f"{name}: unknown initialisation {spec.init!r}")
-        t = t.to(storage)
-        yield name, (t.cpu() if to_cpu else t)
+                   storage: torch.dtype, workers: int = 0) -> Iterator[Tuple[str, torch.Tensor]]:
+    """(name, tensor) for every declared tensor, in name order, each from a CPU generator seeded by
+    (seed, name): values depend neither on the order of generation nor on who asks, so a folder
+    written with a seed and a model built in memory with it hold the same tensors.  Matrices
+    N(0, sigma); biases and norm offsets N(0, 0.02); norm scales 1 + N(0, 0.02).  ``workers`` > 1
+    draws that many tensors at a time on threads (drawing is the slow part of a large model)."""
+    items = sorted(table.items())
+    if workers <= 1 or len(items) < 2:
+        for name, (_, spec) in items:
+            yield name, random_tensor(name, spec, seed, sigma, storage)
+        return
+    from concurrent.futures import ThreadPoolExecutor
+    ahead = 2 * workers                       # tensors drawn but not yet taken: bounds the host memory held
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        pending = []
+        it = iter(items)
+
+        def submit():
+            nxt = next(it, None)
+            if nxt is not None:
+                name, (_, spec) = nxt
+                pending.append((name, pool.submit(random_tensor, name, spec, seed, sigma, storage)))
+
+        for _ in range(ahead):
+            submit()
+        while pending:
+            name, fut = pending.pop(0)
+            submit()
+            yield name, fut.result()
 
 
 def write_model_folder(folder: str, config_dict: dict, table: Dict[str, Tuple[str, ParamSpec]],
-                       seed: int, sigma: float, storage: torch.dtype, device="cpu") -> None:
+                       seed: int, sigma: float, storage: torch.dtype, workers: int = 0) -> None:
     """config.json and model.safetensors of a random model."""
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config_dict, f, indent=2, sort_keys=True)
     write_file(os.path.join(folder, "model.safetensors"),
-               random_tensors(table, seed, sigma, storage, device),
+               random_tensors(table, seed, sigma, storage, workers),
                metadata={"format": "pt", "seed": seed})

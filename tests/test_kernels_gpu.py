@@ -90,7 +90,7 @@ def test_gemm_tcgen05(M, N, K):
     for tile in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
         got = o.gemm_tcgen05(a, w, bias, "gelu_new", add0, add1, out_dtype=torch.float32, tile_n=tile)
         torch.cuda.synchronize()
-        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        assert o.wait_failures()["libgl_gemm_tcgen05"] == 0, "a bounded wait ran out"
         err = (got.double() - ref).abs().max().item()
         assert err <= 3e-5 * max(1.0, ref.abs().max().item()), (tile, err)
     for act in (None, "gelu_new"):
@@ -111,7 +111,7 @@ def test_gemm_tcgen05(M, N, K):
         x = add0.clone()                                               # out = out + product: the add-reduction path
         o.gemm_tcgen05(a, w, bias, "relu", x, out=x, tile_n=tile)
         torch.cuda.synchronize()
-        assert o.wait_failures()["gemm_tcgen05.cu"] == 0
+        assert o.wait_failures()["libgl_gemm_tcgen05"] == 0
         assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item()), tile
 
 
@@ -135,7 +135,7 @@ def _cut_tiles_checks(o, a, w, bias, x0, want, M, N, K):
         x = x0.clone()
         o.gemm_tcgen05(a, w, bias, None, x, out=x, tile_n=tile)
         torch.cuda.synchronize()
-        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        assert o.wait_failures()["libgl_gemm_tcgen05"] == 0, "a bounded wait ran out"
         err = (x.double() - want).abs().max().item()
         assert err <= 3e-5 * max(1.0, want.abs().max().item()), (tile, err)
     # one weight far along K reaches one column exactly, whichever block holds its k-block
@@ -163,7 +163,7 @@ def test_gemm_tcgen05_two_products_one_tile(M, N, K1, K2):
         x = x0.clone()
         o.gemm_tcgen05(a1, w1, b1, None, x, out=x, tile_n=tile, second=(a2, w2, b2))
         torch.cuda.synchronize()
-        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        assert o.wait_failures()["libgl_gemm_tcgen05"] == 0, "a bounded wait ran out"
         err = (x.double() - want).abs().max().item()
         assert err <= 3e-5 * max(1.0, want.abs().max().item()), (tile, err)
     x = x0.clone()
@@ -190,7 +190,7 @@ def test_gemm_tcgen05_two_sets_of_columns(M, N, NB, K):
     for tile in (0, 64, 128, 192, 256, 1256):
         y, yb = o.gemm_tcgen05(a, w, b, None, tile_n=tile, fork=(wb, bb, "gelu_new"))
         torch.cuda.synchronize()
-        assert o.wait_failures()["gemm_tcgen05.cu"] == 0, "a bounded wait ran out"
+        assert o.wait_failures()["libgl_gemm_tcgen05"] == 0, "a bounded wait ran out"
         assert y.shape == (M, N) and yb.shape == (M, NB) and y.dtype == yb.dtype == torch.bfloat16
         for got, ref in ((y, want), (yb, want_b)):
             err = (got.double() - ref).abs().max().item()
@@ -241,7 +241,7 @@ def test_gemm_skinny_two_products_one_output(M, N, K1, K2):
         x = x0.clone()
         o.gemm_skinny(a1, w1, b1, None, x, out=x, split_k=split, second=(a2, w2, b2))
         torch.cuda.synchronize()
-        assert o.wait_failures()["gemm_skinny.cu"] == 0, "a bounded wait ran out"
+        assert o.wait_failures()["libgl_gemm_skinny"] == 0, "a bounded wait ran out"
         err = (x.double() - want).abs().max().item()
         assert err <= 3e-5 * max(1.0, want.abs().max().item()), (split, err)
     x = x0.clone()

@@ -158,12 +158,21 @@ def test_fused_projections_are_taken_in_place_of_split_ones():
 
 def test_resident_types():
     m, v, i = ParamSpec((2, 2)), ParamSpec((2,), "vector"), ParamSpec((2,), "table_int")
-    bf, f32, f16 = torch.bfloat16, torch.float32, torch.float16
+    bf, f32, f16, f64 = torch.bfloat16, torch.float32, torch.float16, torch.float64
     assert resident_dtype(m, bf, bf) == bf            # kept in bfloat16
-    assert resident_dtype(m, f32, bf) == f32          # stored in 32-bit stays so
-    assert resident_dtype(m, f16, bf) == f32
+    assert resident_dtype(m, f16, bf) == bf           # float16 (the published checkpoints) is rounded to bfloat16
+    assert resident_dtype(m, f16, bf, f16) == bf
+    assert resident_dtype(m, f32, bf) == bf           # a checkpoint that declares nothing: brought to the compute type
+    assert resident_dtype(m, f32, bf, f32) == bf      # a 32-bit checkpoint as a whole is rounded
+    assert resident_dtype(m, f64, bf, f32) == bf
+    assert resident_dtype(m, f32, bf, bf) == f32      # stored in 32-bit inside a 16-bit checkpoint: stays so
+    assert resident_dtype(m, f32, bf, f16) == f32
+    assert resident_dtype(m, f16, bf, f16, keep_stored=True) == f32     # the explicit opt-out: exact and slow
+    assert resident_dtype(m, f32, bf, bf, keep_stored=False) == bf
     assert resident_dtype(m, bf, f32) == f32          # the 32-bit path widens everything
+    assert resident_dtype(m, f16, f32) == f32
     assert resident_dtype(v, bf, bf) == f32
+    assert resident_dtype(v, f16, bf, f16) == f32
     assert resident_dtype(i, torch.int64, bf) == torch.int32
     src = tiny.folder("A")
 
@@ -171,9 +180,36 @@ def test_resident_types():
         t["model.layers.0.mlp.fc1.weight"] = t["model.layers.0.mlp.fc1.weight"].float()
     d = rewrite(src, edit)
     _, table = table_for(d)
-    got, nbytes = load_folder(d, table, bf, "cpu")
+    got, nbytes = load_folder(d, table, bf, "cpu", declared=bf)
     assert got["layers/0/ffn/up.weight"].dtype == f32 and got["layers/1/ffn/up.weight"].dtype == bf
     assert got["layers/0/norm/weight"].dtype == f32 and got["embedding"].dtype == bf and nbytes > 0
+
+
+def test_other_stored_types_are_rounded_to_the_compute_type():
+    """A folder stored as float16, and one stored as float32 as a whole, load into bfloat16 matrices
+    that equal the stored values rounded to nearest even; the log says that it happened."""
+    src = tiny.folder("A")
+    _, W = plain_phi.read_folder(src, torch.float32)
+    for stored, label in ((torch.float16, "float16"), (torch.float32, "float32")):
+        def edit(t):
+            for n in t:
+                t[n] = (t[n].float() * 1.003).to(stored)       # values that are not bfloat16 numbers already
+        d = rewrite(src, edit)
+        cfg = json.load(open(os.path.join(d, "config.json")))
+        cfg["torch_dtype"] = label
+        json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+        _, table = table_for(d)
+        said = []
+        got, _ = load_folder(d, table, torch.bfloat16, "cpu", progress=said.append, declared=stored)
+        w = got["layers/1/mixer/q.weight"]
+        assert w.dtype == torch.bfloat16 and got["layers/1/mixer/q.bias"].dtype == torch.float32
+        want = (W["model.layers.1.self_attn.q_proj.weight"] * 1.003).to(stored).to(torch.bfloat16)
+        assert torch.equal(w, want)
+        assert any("rounded to bfloat16" in line and label in line for line in said), said
+        kept, _ = load_folder(d, table, torch.bfloat16, "cpu", declared=stored, keep_stored=True)
+        assert kept["layers/1/mixer/q.weight"].dtype == torch.float32
+        wide, _ = load_folder(d, table, torch.float32, "cpu", declared=stored)
+        assert all(t.dtype == torch.float32 for t in wide.values())
 
 
 def test_random_mode_is_seeded_and_shaped():
@@ -190,6 +226,13 @@ def test_random_mode_is_seeded_and_shaped():
     assert not torch.equal(Wa["lm_head.weight"], Wc["lm_head.weight"])
     w = Wa["model.layers.0.mlp.fc1.weight"]
     assert abs(w.std().item() - 0.02) < 0.002 and abs(w.mean().item()) < 0.002
+    # drawn several tensors at a time or one by one, in a folder or in memory: one seed is one tensor set
+    from gopherllm_b200.weights.loader import random_tensors
+    _, table = table_for(a)
+    one = dict(random_tensors(table, 3, 0.02, torch.bfloat16, workers=0))
+    many = dict(random_tensors(table, 3, 0.02, torch.bfloat16, workers=4))
+    assert list(one) == list(many) == sorted(table)
+    assert all(torch.equal(one[n], many[n]) and torch.equal(one[n].double(), Wa[n]) for n in one)
     g = Wa["model.layers.1.input_layernorm.weight"]
     assert abs(g.mean().item() - 1.0) < 0.02 and 0.005 < g.std().item() < 0.04
     assert 0.005 < Wa["model.layers.1.self_attn.dense.bias"].std().item() < 0.04

@@ -57,3 +57,56 @@ def close(got, ref, dtype):
     err = np.abs(got - ref).max()
     bound = TOL[dtype] * max(1.0, np.abs(ref).max())
     return err, bound
+
+
+# --------------------------------------------------------------------------
+# a model whose next-token logits hang on one far key and on the positions
+# --------------------------------------------------------------------------
+FAR_KEY = dict(TINY_A, max_position_embeddings=320, vocab_size=300)
+FAR_TOKEN = 7          # the token whose key stands out; prompts hold it once, early
+_FAR = {}
+
+
+def far_key_folder():
+    """Tiny configuration A with 320 positions and weights made so that random weights cannot hide a
+    wrong rotation, a wrong position or a missed far key.  In layer 0, head 0, one rotary pair (dims
+    1 and 5 of 16, angle 0.1 a position): every query has a large bias in dim 1, and the key's row
+    for dim 1 points along the normalised embedding of FAR_TOKEN, so wherever that token sits its
+    key scores 8*cos(0.1 * distance) while other keys score about 0.  The same token's value in that
+    head is large and the output projection is not small, so the residual stream after layer 0, and
+    with it the logits, swing with the distance to that one position."""
+    if "d" in _FAR:
+        return _FAR["d"]
+    import json
+    import math
+    import torch
+    from gopherllm_b200 import write_random_model
+    import plain_phi
+    d = tempfile.mkdtemp(prefix="gl_tiny_far_")
+    write_random_model(d, dict(FAR_KEY), seed=9)
+    cfg, W = plain_phi.read_folder(d, torch.float32)
+    hd, D = 16, FAR_KEY["hidden_size"]
+    pre = "model.layers.0."
+    n = plain_phi.layer_norm(W["model.embed_tokens.weight"][FAR_TOKEN], W[pre + "input_layernorm.weight"],
+                             W[pre + "input_layernorm.bias"], cfg["layer_norm_eps"])
+    unit = n / (n * n).sum()
+    amp = math.sqrt(8.0 * math.sqrt(hd))               # amp^2 / sqrt(hd) = 8
+    W[pre + "self_attn.k_proj.weight"][1] = amp * unit
+    W[pre + "self_attn.k_proj.bias"][1] = 0.0
+    W[pre + "self_attn.q_proj.weight"][1] = 0.0
+    W[pre + "self_attn.q_proj.bias"][1] = amp
+    g = torch.Generator().manual_seed(77)
+    u = torch.randn(hd, generator=g)
+    W[pre + "self_attn.v_proj.weight"][:hd] += 3.0 * u[:, None] * unit[None, :]
+    W[pre + "self_attn.dense.weight"][:, :hd] *= 4.0
+    from gopherllm_b200.weights.safetensors_io import write_file
+    write_file(os.path.join(d, "model.safetensors"), ((k, v.to(torch.bfloat16)) for k, v in sorted(W.items())))
+    _FAR["d"] = d
+    return d
+
+
+def far_key_prompt(rng, n, at=3):
+    """n tokens without FAR_TOKEN except at position ``at``."""
+    toks = [int(t) for t in rng.integers(8, FAR_KEY["vocab_size"], size=n)]
+    toks[at] = FAR_TOKEN
+    return toks
