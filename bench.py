@@ -238,8 +238,7 @@ def main():
             times.append(e0.elapsed_time(e1))
             eng.close(s)
         ms = min(times)
-        layer_params = sum(t.numel() for b in eng.model.blocks for t in
-                           (b.mixer.w_qkv, b.mixer.w_out, b.ffn.w_up, b.ffn.w_down))
+        layer_params = sum(w.numel() for e in spec.schedule for _, w, _, _ in eng.model.blocks[e.layer].products())
         flops = 2.0 * T * layer_params + 2.0 * T * T * cfg["hidden_size"] * layers + 2.0 * V * cfg["hidden_size"]
         out["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
                           "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}

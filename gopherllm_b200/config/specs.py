@@ -94,6 +94,10 @@ class BlockSpec:
     mixer: MixerSpec
     ffn: FeedForwardSpec
     norm2: Optional[NormSpec] = None
+    extra: Tuple[Tuple[str, object], ...] = ()   # free-form options for other arrangements (further norms, branches)
+
+    def option(self, key, default=None):
+        return dict(self.extra).get(key, default)
 
 
 @dataclass(frozen=True)
@@ -118,8 +122,19 @@ class ModelSpec:
     head_bias: bool = True
     embedding_scale: float = 1.0
     stop_tokens: Tuple[int, ...] = ()
+    # learned absolute positions: a table of this many rows added to the embeddings before the first
+    # layer (model.go:2648-2651); 0: none
+    position_table: int = 0
+    # logits * logit_scale, then softcap * tanh(logits / softcap) when softcap > 0 (model.go:2555-2564)
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0
 
     def __post_init__(self):
+        if self.position_table and self.position_table < self.max_positions:
+            raise ValueError(f"a position table of {self.position_table} rows does not cover "
+                             f"{self.max_positions} positions")
+        if self.logit_softcap < 0 or not self.logit_scale > 0:
+            raise ValueError("logit_softcap must be >= 0 and logit_scale > 0")
         for e in self.schedule:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}, model has {len(self.layers)}")

@@ -20,7 +20,7 @@
 namespace cg = cooperative_groups;
 
 #ifndef GL_HEAD_DIM
-#define GL_HEAD_DIM 80
+#error "compile with -DGL_HEAD_DIM=<head size>: this file is built once per head size a model uses, and knows none itself"
 #endif
 static_assert(GL_HEAD_DIM % 16 == 0 && GL_HEAD_DIM >= 16 && GL_HEAD_DIM <= 256, "head size: 16..256 in steps of 16");
 
@@ -35,6 +35,7 @@ static_assert(GL_HEAD_DIM % 16 == 0 && GL_HEAD_DIM >= 16 && GL_HEAD_DIM <= 256, 
 #endif
 #define AD_MAXG 8                                   // query heads per key/value head (the 8 columns of the MMA)
 
+#define GL_DECODE_ARGS_DEFINED      // (attention_decode_static.h declares the same layout for C hosts)
 struct DecodeArgs {
     const __nv_bfloat16* q;      // [B, nH*hd], scaled
     __nv_bfloat16* out;          // [B, nH*hd]
@@ -459,7 +460,9 @@ static int decode_checked(const DecodeArgs& a, const DecodeQkv& x, cudaStream_t 
 static __device__ __align__(256) float gl_decode_static_scratch[GL_DECODE_STATIC_SCRATCH_FLOATS];
 
 #define GL_DECODE_STATIC_MAX_DEVICES 64
-static float* gl_decode_static_ptr[GL_DECODE_STATIC_MAX_DEVICES];   // device address of the array, per device
+// device address of the array, per device; written once per device with a value that is the same
+// whichever thread writes it, so first calls from two threads need no lock
+static float* gl_decode_static_ptr[GL_DECODE_STATIC_MAX_DEVICES];
 
 GL_API long long gl_attention_decode_static_capacity() { return GL_DECODE_STATIC_SCRATCH_FLOATS; }
 

@@ -30,16 +30,40 @@
 //    it has to start at zero: each call writes every cell it later reads.  Two calls
 //    that overlap on the GPU (different streams, or the same library used from two
 //    threads without ordering) race on it; order them on one stream or with events.
+//  * The per-device address is looked up by whichever thread calls first on that device and
+//    kept in a plain array.  Two threads that both make a device's first call both look it
+//    up and store the same value; no lock is taken and none is needed.
+//
+// The header stands alone: a C host includes it, fills in a DecodeArgs and calls.
 #pragma once
 
+#include <cuda_runtime.h>
+
 #define GL_DECODE_STATIC_SCRATCH_FLOATS (1 << 20)
+
+#ifndef GL_DECODE_ARGS_DEFINED
+#define GL_DECODE_ARGS_DEFINED
+// The argument record of decode attention as a C host sees it (the library's own source
+// declares the same layout with typed pointers).  bfloat16 values are 16-bit words.
+struct DecodeArgs {
+    const void* q;        // [B, nH*hd] bfloat16 queries, already rotated and scaled
+    void* out;            // [B, nH*hd] bfloat16
+    const void* k_cache;  // [pages, nKV, 64, hd] bfloat16
+    const void* v_cache;  // the same shape
+    const int* seq_ctx;   // [B] positions cached before this step (the new token's key sits at seq_ctx[b])
+    const int* pages;     // [B, max_pages] page numbers of each sequence
+    float* part_o;        // ignored by gl_attention_decode_static
+    float* part_ml;       // ignored by gl_attention_decode_static
+    int B, nH, nKV, max_pages, window, splits;
+};
+#endif
 
 #ifdef __cplusplus
 extern "C" {
 #endif
-struct DecodeArgs;
 int gl_attention_decode_static(const struct DecodeArgs* args, cudaStream_t stream);
 long long gl_attention_decode_static_capacity(void);
+long long gl_attention_decode_scratch(int B, int nH, int splits);
 #ifdef __cplusplus
 }
 #endif

@@ -11,7 +11,7 @@
 #include "common.cuh"
 
 #ifndef GL_HEAD_DIM
-#define GL_HEAD_DIM 80
+#error "compile with -DGL_HEAD_DIM=<head size>: this file is built once per head size a model uses, and knows none itself"
 #endif
 static_assert(GL_HEAD_DIM % 16 == 0 && GL_HEAD_DIM >= 16 && GL_HEAD_DIM <= 256, "head size: 16..256 in steps of 16");
 

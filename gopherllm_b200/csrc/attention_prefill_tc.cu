@@ -32,7 +32,7 @@
 #include "tcgen05.cuh"
 
 #ifndef GL_HEAD_DIM
-#define GL_HEAD_DIM 80
+#error "compile with -DGL_HEAD_DIM=<head size>: this file is built once per head size a model uses, and knows none itself"
 #endif
 static_assert(GL_HEAD_DIM % 16 == 0 && GL_HEAD_DIM >= 16 && GL_HEAD_DIM <= 128, "head size: 16..128 in steps of 16");
 static_assert(GL_PAGE == 64, "a step is one page of 64 keys");
@@ -86,19 +86,6 @@ struct AttnArgs {
 };
 
 struct AttnMaps { CUtensorMap q[4], k[4], v; };
-
-// Measurement only (AT_PROFILE): clocks the first row thread of block 0 spends in each phase of a page
-// (waiting for scores, loading them, maximum, rescaling, exp and store, hand-over).
-#ifdef AT_PROFILE
-__device__ long long at_prof[32];
-#define AT_PROF_BEGIN(on) const bool prof_on = (on); long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
-#define AT_T(i) { long long now_ = clock64(); if (prof_on) prof[i] += now_ - t_last; t_last = now_; }
-#define AT_PROF_END(base) if (prof_on) { for (int i_ = 0; i_ < 8; ++i_) at_prof[(base) + i_] = prof[i_]; }
-#else
-#define AT_PROF_BEGIN(on)
-#define AT_T(i)
-#define AT_PROF_END(base)
-#endif
 
 __device__ __forceinline__ float at_exp2(float x) {
     float y;
@@ -272,16 +259,13 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
         const float LOG2E = 1.4426950408889634f;
         float m_run = -INFINITY, l_run = 0.f;
         bool alive = true;
-        AT_PROF_BEGIN(threadIdx.x == 0 && blockIdx.x == 0)
         for (int j = 0; j < nt; ++j) {
             const int st = j % AT_STAGES;
             const int j0 = (page_begin + j) * GL_PAGE;
-            AT_T(7)
             bool ok = mbar_wait(BAR_SF(t, j & 1), (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { failed = 1; alive = false; break; }
             tc_fence_after();
-            AT_T(0)
             float sc[GL_PAGE];
             {
                 unsigned (&su)[GL_PAGE] = reinterpret_cast<unsigned (&)[GL_PAGE]>(sc);
@@ -289,7 +273,6 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
                 tmem_ld32_issue(tS + 64 * (j & 1) + 32, *reinterpret_cast<unsigned (*)[32]>(&su[32]));
                 tmem_ld_wait();
             }
-            AT_T(1)
             if (j0 + GL_PAGE - 1 > pos || j0 < wlo) {                       // a row at x sees keys max(0, x-window+1)..x
 #pragma unroll
                 for (int i = 0; i < GL_PAGE; ++i)
@@ -315,7 +298,6 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
                 m_run = m_new;
             }
             const float mu = (m_run == -INFINITY) ? 0.f : m_run * LOG2E;
-            AT_T(2)
             if (rescale && j >= 1) {
                 ok = mbar_wait(BAR_PD(t), (j - 1) & 1);                     // the products so far are complete
                 ok = __all_sync(0xffffffffu, ok);
@@ -330,7 +312,6 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
                     tmem_st16(tO + c, t16);
                 }
             }
-            AT_T(3)
             // weights as bfloat16 over the first half of the scores they came from, two a column
             float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -347,7 +328,6 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
                 tmem_st16(tS + 64 * (j & 1) + c / 2, pk);
             }
             l_run = l_run * corr + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
-            AT_T(4)
             // rows of the page past the sequence were never written: they must not reach the product
             // (both tiles may clear the same rows; they write the same zeros)
             if (j0 + GL_PAGE > total) {
@@ -367,12 +347,7 @@ attn_prefill_tc_kernel(AttnArgs a, const __grid_constant__ AttnMaps maps) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(BAR_PF(t, j & 1));
-            AT_T(5)
         }
-        AT_PROF_END(0)
-#ifdef AT_PROFILE
-        if (prof_on) at_prof[8] = nt;
-#endif
         if (alive && nt > 0) {
             bool ok = mbar_wait(BAR_OF(t), 0);
             ok = __all_sync(0xffffffffu, ok);
@@ -417,11 +392,6 @@ static size_t at_smem() {
 GL_API int gl_attention_prefill_tc_head_dim() { return AT_HD; }
 
 
-#ifdef AT_PROFILE
-GL_API int gl_attention_prefill_tc_profile(long long* out) {
-    return cudaMemcpyFromSymbol(out, at_prof, sizeof(long long) * 32) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 GL_API int gl_attention_prefill_tc_wait_failed() {
     int v = 0;

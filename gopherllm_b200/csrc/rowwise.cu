@@ -35,6 +35,58 @@ GL_API int gl_embed(const void* table, int table_dtype, const int* tokens, float
 }
 
 // ---------------------------------------------------------------------------
+// A second table added onto the residual stream: out[t, :] += table[index[t], :].  Learned
+// absolute positions are added once, before the first layer (model.go:2648-2651).
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void add_rows_kernel(const TW* __restrict__ table, const int* __restrict__ index,
+                                float* __restrict__ out, int D, int N) {
+    const int t = blockIdx.x;
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    int i = index[t];
+    i = i < 0 ? 0 : (i >= N ? N - 1 : i);        // checked on the host; never read outside the table
+    const TW* row = table + (size_t)i * D;
+    float* o = out + (size_t)t * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] += gl_load(row + d);
+}
+
+GL_API int gl_add_rows(const void* table, int table_dtype, const int* index, float* out,
+                       int T, int D, int N, cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (D <= 0 || N <= 0) return GL_ERR_SHAPE;
+    const int threads = D >= 1024 ? 256 : 128;
+    if (table_dtype == GL_F32)
+        return gl_launch(add_rows_kernel<float>, dim3(T), dim3(threads), 0, stream, 1, (const float*)table, index, out, D, N);
+    if (table_dtype == GL_BF16)
+        return gl_launch(add_rows_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 1,
+                         (const __nv_bfloat16*)table, index, out, D, N);
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Logits in place: x <- x * scale, then x <- cap * tanh(x / cap) if cap > 0 (the reference's
+// LogitScale and final soft cap, model.go:2555-2564).  32-bit throughout.
+// ---------------------------------------------------------------------------
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t n, float scale, float cap) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v / cap);
+        x[i] = v;
+    }
+}
+
+GL_API int gl_scale_softcap(float* x, long long n, float scale, float cap, cudaStream_t stream) {
+    if (n <= 0) return GL_OK;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want > 4096 ? 4096 : want);
+    return gl_launch(scale_softcap_kernel, dim3(blocks), dim3(threads), 0, stream, 1, x, (size_t)n, scale, cap);
+}
+
+// ---------------------------------------------------------------------------
 // Normalisation of selected rows of a 32-bit matrix.
 //   layernorm: mean, biased variance over the row, y = (x-mean)*rsqrt(var+eps)*g + b
 //              (bert.go:748-776; the reference takes 1/sqrt in 64-bit, so does this)

@@ -43,19 +43,17 @@ def kernel_bench_rows(model, runs: int, layer: int, batch: int = 1) -> List[dict
     row("token_embd.row", net.embedding, lambda: ops.embed(net.embedding, toks))
     if net.blocks:
         blk = net.blocks[max(0, min(layer, len(net.blocks) - 1))]
-        mixer, ffn = blk.mixer, blk.ffn
 
         def x(n):
             return (torch.arange(batch * n, device=dev, dtype=torch.float32).reshape(batch, n) % 17 - 8).mul(0.01).to(dt)
 
-        if hasattr(mixer, "w_qkv"):
-            xin, xo = x(mixer.w_qkv.shape[1]), x(mixer.w_out.shape[1])
-            row("attn_qkv", mixer.w_qkv, lambda: ops.linear(xin, mixer.w_qkv, mixer.b_qkv, out_dtype=dt))
-            row("attn_output", mixer.w_out, lambda: ops.linear(xo, mixer.w_out, mixer.b_out, out_dtype=torch.float32))
-        if hasattr(ffn, "w_up"):
-            xu, xd = x(ffn.w_up.shape[1]), x(ffn.w_down.shape[1])
-            row("ffn_up", ffn.w_up, lambda: ops.linear(xu, ffn.w_up, ffn.b_up, act=ffn.spec.activation, out_dtype=dt))
-            row("ffn_down", ffn.w_down, lambda: ops.linear(xd, ffn.w_down, ffn.b_down, out_dtype=torch.float32))
+        # every product the layer's parts declare, whatever kinds they are: each as the kernel a step
+        # of ``batch`` tokens would launch for it
+        for name, w, b, act in blk.products():
+            xin = x(w.shape[1])
+            # a product as wide as the model adds onto the 32-bit residual stream; others feed the next product
+            out_dt = torch.float32 if w.shape[0] == net.spec.hidden else dt
+            row(name.replace(".", "_"), w, lambda xin=xin, w=w, b=b, act=act, out_dt=out_dt: ops.linear(xin, w, b, act=act, out_dtype=out_dt))
     xh = (torch.ones(batch, net.head_weight.shape[1], device=dev) * 0.01).to(dt)
     row("output", net.head_weight, lambda: ops.linear(xh, net.head_weight, net.head_bias, out_dtype=torch.float32))
     return rows

@@ -21,6 +21,7 @@ class DecoderModel:
         self.blocks = [build_block(b) for b in spec.layers]
         self.final_norm = build_norm(spec.final_norm)
         self.embedding: Optional[torch.Tensor] = None
+        self.positions: Optional[torch.Tensor] = None          # learned absolute positions, if the spec has them
         self.head_weight: Optional[torch.Tensor] = None
         self.head_bias: Optional[torch.Tensor] = None
 
@@ -31,6 +32,8 @@ class DecoderModel:
         for i, b in enumerate(self.blocks):
             for k, v in b.parameters().items():
                 p[f"layers/{i}/{k}"] = v
+        if s.position_table:
+            p["positions"] = ParamSpec((s.position_table, s.hidden))
         for k, v in self.final_norm.parameters().items():
             p[f"final_norm/{k}"] = v
         if not s.tie_embeddings:
@@ -42,6 +45,7 @@ class DecoderModel:
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.embedding = tensors["embedding"]
+        self.positions = tensors["positions"] if self.spec.position_table else None
         for i, b in enumerate(self.blocks):
             pre = f"layers/{i}/"
             b.load({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)})
@@ -65,6 +69,7 @@ class DecoderModel:
 
     def _all_tensors(self):
         yield self.embedding
+        yield self.positions
         yield self.head_weight
         yield self.head_bias
         stack = list(self.blocks) + [self.final_norm]
@@ -101,7 +106,10 @@ class DecoderModel:
     # The same step in three pieces, for a caller that captures it as more than one CUDA graph.
     def begin(self, ctx) -> torch.Tensor:
         """The residual stream of the step's tokens, float32 [tokens, hidden]."""
-        return ops.embed(self.embedding, ctx.tokens, self.spec.embedding_scale)
+        x = ops.embed(self.embedding, ctx.tokens, self.spec.embedding_scale)
+        if self.positions is not None:
+            ops.add_rows(self.positions, ctx.tok_pos, x)
+        return x
 
     def run(self, x, ctx, cache, start: int, stop: int) -> None:
         """Runs start..stop-1 of the schedule, updating x in place."""
@@ -114,4 +122,7 @@ class DecoderModel:
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab), dtype=torch.float32, device=x.device)
         xn = self.final_norm.forward(x, ctx.act_dtype, rows=ctx.want_rows)
-        return ops.linear(xn, self.head_weight, self.head_bias, out_dtype=torch.float32)
+        logits = ops.linear(xn, self.head_weight, self.head_bias, out_dtype=torch.float32)
+        if s.logit_scale != 1.0 or s.logit_softcap > 0.0:
+            ops.scale_softcap(logits, s.logit_scale, s.logit_softcap)
+        return logits

@@ -113,6 +113,26 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0,
     return out
 
 
+def add_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] += table[index[t]] (float32 rows; a table of learned positions added to the residual stream)."""
+    _need(table, "table")
+    _need(index, "index", torch.int32)
+    N, D = table.shape
+    _need(out, "out", torch.float32, (index.numel(), D))
+    fn = _lib("rowwise.cu").gl_add_rows
+    _check(fn(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(index), _ptr(out),
+              c_int(index.numel()), c_int(D), c_int(N), _stream()), "add_rows")
+    return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """In place on float32 logits: x * scale, then cap * tanh(x / cap) when cap > 0."""
+    _need(x, "x", torch.float32)
+    fn = _lib("rowwise.cu").gl_scale_softcap
+    _check(fn(_ptr(x), ctypes.c_longlong(x.numel()), c_float(scale), c_float(cap), _stream()), "scale_softcap")
+    return x
+
+
 def norm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps: float,
          out_dtype: torch.dtype, rms: bool = False, rows: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -330,7 +350,7 @@ def decode_blocks_per_sm(head_dim: int, group: int = 1) -> int:
     return max(1, min(8, (227 * 1024) // (smem + 1024)))
 
 
-def decode_splits(batch: int, num_kv_heads: int, max_len: int, device, head_dim: int = 80,
+def decode_splits(batch: int, num_kv_heads: int, max_len: int, device, head_dim: int,
                   group: int = 1) -> int:
     """How many blocks share one (sequence, key/value head).  Never more blocks than are resident
     at once (a grid a little larger than the machine would run a second, nearly empty wave), never

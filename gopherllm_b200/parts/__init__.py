@@ -5,3 +5,4 @@ from .base import (Block, FeedForward, KVRequest, Mixer, Norm, ParamSpec, Part, 
                    build_position, register_block, register_feed_forward, register_mixer,
                    register_norm, register_position)
 from . import norms, position, attention, feedforward, block  # register the built-in kinds
+from .block import AssembledBlock

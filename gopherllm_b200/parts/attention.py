@@ -78,6 +78,9 @@ class Attention(Mixer):
     def first_product(self):
         return self.w_qkv, self.b_qkv, None
 
+    def products(self):
+        return [("qkv", self.w_qkv, self.b_qkv, None), ("out", self.w_out, self.b_out, None)]
+
     def until_last(self, xn, ctx, cache, first=None):
         """Everything but the output projection: the attention output [T, heads * head size] with the
         projection's weight and bias.  ``first``: the joined q, k, v projection if the caller made it."""

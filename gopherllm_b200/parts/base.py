@@ -67,6 +67,12 @@ class Part:
         for k, v in tensors.items():
             setattr(self, "p_" + k.replace(".", "_"), v)
 
+    def products(self) -> List[Tuple[str, torch.Tensor, Optional[torch.Tensor], Optional[str]]]:
+        """The matrix products this part makes for every token, as (name, weight [out, in], bias,
+        activation), in the order it makes them; for measurement (flop counts, isolated kernel
+        timing) by code that does not know the part's kind.  Parts may leave it empty."""
+        return []
+
 
 class Norm(Part):
     """forward(x float32 [R, D], out_dtype, rows=None) -> [R', D] of out_dtype."""

@@ -10,7 +10,13 @@ from ..config.specs import BlockSpec
 from .base import Block, ParamSpec, build_feed_forward, build_mixer, build_norm, register_block
 
 
-class _AssembledBlock(Block):
+class AssembledBlock(Block):
+    """A block put together from child parts.  ``children()`` says which: a dict from slot name to
+    part, in a fixed order; parameters, loading and the capture flag walk it, so an arrangement with
+    more parts (a norm after a branch, a third branch) overrides ``children`` and ``forward`` and
+    nothing else.  A parameter's key is "<slot>/<the child's own key>".  This base builds the usual
+    four from the spec: ``norm``, ``mixer``, ``ffn`` and, if the spec has one, ``norm2``."""
+
     def __init__(self, spec: BlockSpec):
         self.spec = spec
         self.norm = build_norm(spec.norm)
@@ -18,31 +24,35 @@ class _AssembledBlock(Block):
         self.mixer = build_mixer(spec.mixer)
         self.ffn = build_feed_forward(spec.ffn)
 
-    def _children(self):
-        yield "norm", self.norm
+    def children(self) -> Dict[str, object]:
+        c = {"norm": self.norm}
         if self.norm2 is not None:
-            yield "norm2", self.norm2
-        yield "mixer", self.mixer
-        yield "ffn", self.ffn
+            c["norm2"] = self.norm2
+        c["mixer"] = self.mixer
+        c["ffn"] = self.ffn
+        return c
 
     def parameters(self) -> Dict[str, ParamSpec]:
-        """Keys are "<slot>/<parameter>": the slot names the child part."""
-        return {f"{slot}/{k}": v for slot, part in self._children() for k, v in part.parameters().items()}
+        return {f"{slot}/{k}": v for slot, part in self.children().items() for k, v in part.parameters().items()}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        for slot, part in self._children():
+        for slot, part in self.children().items():
             pre = slot + "/"
             part.load({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)})
 
     def cache_request(self):
         return self.mixer.cache_request()
 
+    def products(self):
+        return [(f"{slot}.{name}", w, b, act) for slot, part in self.children().items()
+                for name, w, b, act in part.products()]
+
     @property
     def capturable(self):
-        return all(part.capturable for _, part in self._children())
+        return all(part.capturable for part in self.children().values())
 
 
-class ParallelBlock(_AssembledBlock):
+class ParallelBlock(AssembledBlock):
     """x ← (x + ffn(n)) + mixer(n), n = norm(x): one norm feeds both branches
     (model.go:2738-2740) and both are added to the residual, the feed-forward
     first (model.go:2812-2815)."""
@@ -106,7 +116,7 @@ class ParallelBlock(_AssembledBlock):
         return x
 
 
-class SequentialBlock(_AssembledBlock):
+class SequentialBlock(AssembledBlock):
     """x ← x + mixer(norm(x)); x ← x + ffn(norm2(x)) (model.go:2806-2811)."""
 
     def __init__(self, spec: BlockSpec):

@@ -38,6 +38,9 @@ class DenseFeedForward(FeedForward):
     def first_product(self):
         return self.w_up, self.b_up, self.spec.activation
 
+    def products(self):
+        return [("up", self.w_up, self.b_up, self.spec.activation), ("down", self.w_down, self.b_down, None)]
+
     def until_last(self, xn, ctx, first=None):
         h = first if first is not None else ops.linear(xn, self.w_up, self.b_up, act=self.spec.activation,
                                                        out_dtype=ctx.act_dtype)

@@ -39,19 +39,25 @@ class WeightsError(ValueError):
 
 
 def tensor_table(model_parameters: Dict[str, ParamSpec], names) -> Dict[str, Tuple[str, ParamSpec]]:
-    """file tensor name -> (model parameter key, spec).  Keys are "embedding",
-    "final_norm/<p>", "head/<p>" and "layers/<i>/<slot>/<p>"."""
+    """file tensor name -> (model parameter key, spec).  Keys are "embedding", "positions",
+    "final_norm/<p>", "head/<p>" and "layers/<i>/<slot>/<p>", where <p> may itself be a path
+    ("sub/weight": a part inside the slot's part); ``names.layer`` gets it with dots for slashes,
+    the way a part spells its own nested parameters ("q_norm.weight")."""
     table: Dict[str, Tuple[str, ParamSpec]] = {}
     for key, spec in model_parameters.items():
         parts = key.split("/")
-        if parts[0] == "embedding":
+        if parts[0] == "embedding" and len(parts) == 1:
             name = names.embedding
-        elif parts[0] == "final_norm":
-            name = f"{names.final_norm}.{parts[1]}"
-        elif parts[0] == "head":
-            name = f"{names.head}.{parts[1]}"
-        elif parts[0] == "layers":
-            name = names.layer(int(parts[1]), parts[2], parts[3])
+        elif parts[0] == "positions" and len(parts) == 1:
+            name = getattr(names, "positions", None)
+            if name is None:
+                raise KeyError("the model has a position table but its tensor names give no `positions`")
+        elif parts[0] == "final_norm" and len(parts) >= 2:
+            name = f"{names.final_norm}.{'.'.join(parts[1:])}"
+        elif parts[0] == "head" and len(parts) >= 2:
+            name = f"{names.head}.{'.'.join(parts[1:])}"
+        elif parts[0] == "layers" and len(parts) >= 4:
+            name = names.layer(int(parts[1]), parts[2], ".".join(parts[3:]))
         else:
             raise KeyError(f"model parameter {key!r} has no tensor name")
         if name in table:

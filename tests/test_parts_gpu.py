@@ -498,3 +498,127 @@ def test_toy_routed_feed_forward_and_position_registered_built_and_stepped(dtype
     for sl in slots:
         m.close_sequence(sl)
     assert bad == 0 if dtype == "float32" else bad <= rows // 10, (bad, rows)
+
+
+# --------------------------------------------------------------------------
+# A block arrangement of its own (a norm after the mixer as well as before it), learned absolute
+# positions and scaled, soft-capped logits: a toy again, registered and run without a change to
+# the package.
+def define_toy_sandwich():
+    from gopherllm_b200.config import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec)
+    from gopherllm_b200.config.registry import Architecture, register_architecture, resolve_architecture
+    from gopherllm_b200.config.specs import default_schedule
+    from gopherllm_b200.parts import AssembledBlock, build_norm, register_block
+
+    class SandwichBlock(AssembledBlock):
+        """x <- x + post_norm(mixer(norm(x))); x <- x + ffn(norm2(x)).  One child more than the usual
+        four; parameters, loading and the capture flag come from ``children``."""
+
+        def __init__(self, spec):
+            super().__init__(spec)
+            self.post_norm = build_norm(spec.option("post_norm"))
+
+        def children(self):
+            c = super().children()
+            c["post_norm"] = self.post_norm
+            return c
+
+        def forward(self, x, ctx, cache):
+            h = torch.empty_like(x)
+            self.mixer.forward(self.norm.forward(x, ctx.act_dtype), ctx, cache, (), h)
+            x.add_(self.post_norm.forward(h, torch.float32))
+            self.ffn.forward(self.norm2.forward(x, ctx.act_dtype), ctx, (x,), x)
+            return x
+
+    if resolve_architecture("toy-sandwich") is None:
+        register_block("sandwich", SandwichBlock)
+
+        @dataclass
+        class SandwichConfig:
+            hidden_size: int = 56
+            vocab_size: int = 83
+            positions: int = 96
+            torch_dtype: str = "bfloat16"
+            initializer_range: float = 0.15
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__})
+
+            def to_dict(self):
+                return dict(architectures=["ToySandwichForCausalLM"], model_type="toy-sandwich", **self.__dict__)
+
+        def spec_of(c):
+            norm = NormSpec("layernorm", c.hidden_size, 1e-5, bias=True)
+            post = NormSpec("rmsnorm", c.hidden_size, 1e-6, bias=False)
+            att = MixerSpec("attention", c.hidden_size, 2, 1, 32, 0, 32 ** -0.5, False, None, PositionSpec("none"))
+            ffn = FeedForwardSpec("dense", c.hidden_size, 72, "gelu", True)
+            block = BlockSpec("sandwich", norm, att, ffn, norm, extra=(("post_norm", post),))
+            return ModelSpec(c.hidden_size, c.vocab_size, c.positions, (block, block), default_schedule(2), norm,
+                             tie_embeddings=False, head_bias=False, embedding_scale=2.0,
+                             position_table=c.positions, logit_scale=0.5, logit_softcap=3.0)
+
+        class Names:
+            embedding, final_norm, head, positions = "wte.weight", "ln_f", "head", "wpe.weight"
+
+            def __init__(self, c):
+                pass
+
+            def layer(self, i, slot, key):
+                return f"h.{i}.{slot}.{key}"
+
+        register_architecture(Architecture("toy-sandwich", SandwichConfig, spec_of, Names), aliases=["ToySandwich"])
+    return resolve_architecture("toy-sandwich")
+
+
+def toy_sandwich_plain(tokens, W):
+    T = len(tokens)
+    x = 2.0 * W["wte.weight"][torch.tensor(tokens)] + W["wpe.weight"][:T]
+    for i in range(2):
+        p = f"h.{i}."
+        n = plain_phi.layer_norm(x, W[p + "norm.weight"], W[p + "norm.bias"], 1e-5)
+        q = (n @ W[p + "mixer.q.weight"].T).reshape(T, 2, 32) * 32 ** -0.5
+        k = (n @ W[p + "mixer.k.weight"].T).reshape(T, 1, 32)
+        v = (n @ W[p + "mixer.v.weight"].T).reshape(T, 1, 32)
+        h = plain_phi.attention(q, k, v).reshape(T, 64) @ W[p + "mixer.out.weight"].T
+        x = x + h / torch.sqrt((h * h).mean(-1, keepdim=True) + 1e-6) * W[p + "post_norm.weight"]
+        n2 = plain_phi.layer_norm(x, W[p + "norm2.weight"], W[p + "norm2.bias"], 1e-5)
+        x = x + plain_phi.mlp(n2, W[p + "ffn.up.weight"], W[p + "ffn.up.bias"], W[p + "ffn.down.weight"],
+                              W[p + "ffn.down.bias"], "gelu")
+    logits = plain_phi.layer_norm(x, W["ln_f.weight"], W["ln_f.bias"], 1e-5) @ W["head.weight"].T
+    return 3.0 * torch.tanh(logits * 0.5 / 3.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_block_with_a_norm_after_its_mixer_positions_table_and_capped_logits(dtype):
+    import gopherllm_b200 as gl
+    arch = define_toy_sandwich()
+    cfg = arch.config_class()
+    folder = tempfile.mkdtemp(prefix="gl_toy_sandwich_")
+    gl.write_random_model(folder, cfg.to_dict(), seed=8)
+    m = gl.load(folder, dtype=dtype, max_tokens=512)
+    assert m.architecture.name == "toy-sandwich"
+    keys = m.engine.model.parameters()
+    assert "layers/1/post_norm/weight" in keys and "positions" in keys
+    _, W = plain_phi.read_folder(folder)
+    assert "h.1.post_norm.weight" in W and "wpe.weight" in W
+    rng = np.random.default_rng(9)
+    seqs = [tiny.prompt(rng, n, cfg.vocab_size) for n in (70, 11)]
+    refs = [toy_sandwich_plain(s, W).numpy() for s in seqs]
+    assert max(np.abs(r).max() for r in refs) > 1.0             # the cap is at work
+    tol = dict(float32=2e-4, bfloat16=3e-2)[dtype]
+    slots = [m.open_sequence() for _ in seqs]
+    cut = [50, 6]
+    out = m.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], [list(range(c)) for c in cut]).cpu().numpy()
+    o = 0
+    for i, c in enumerate(cut):
+        assert np.abs(out[o:o + c] - refs[i][:c]).max() <= tol * max(1.0, np.abs(refs[i]).max()), i
+        o += c
+    for t in range(max(len(s) - c for s, c in zip(seqs, cut))):          # decode steps (captured in bfloat16)
+        live = [i for i in range(2) if cut[i] + t < len(seqs[i])]
+        got = m.step([(slots[i], [seqs[i][cut[i] + t]]) for i in live]).cpu().numpy()
+        for r, i in enumerate(live):
+            assert np.abs(got[r] - refs[i][cut[i] + t]).max() <= tol * max(1.0, np.abs(refs[i]).max()), (i, t)
+    for sl in slots:
+        m.close_sequence(sl)
+    m.engine.cache.check()

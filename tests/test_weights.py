@@ -243,3 +243,23 @@ def test_random_mode_is_seeded_and_shaped():
     assert abs(Wd["model.layers.0.mlp.fc1.weight"].std().item() - 0.05) < 0.004      # initializer_range
     model, table = table_for(d)
     check_folder(d, table)
+
+
+def test_deeper_parameter_keys_reach_the_names_or_are_refused():
+    """A part nested inside a slot's part declares "sub/weight": the tensor table hands the names
+    "sub.weight" (not a truncated key); a key no rule covers is an error."""
+    from gopherllm_b200.parts import ParamSpec
+    from gopherllm_b200.weights.loader import tensor_table
+
+    class Names:
+        embedding, final_norm, head = "e", "fn", "hd"
+
+        def layer(self, i, slot, key):
+            return f"L{i}.{slot}.{key}"
+    t = tensor_table({"embedding": ParamSpec((4, 2)), "layers/3/mixer/inner/gate/weight": ParamSpec((2, 2)),
+                      "final_norm/weight": ParamSpec((2,), "vector")}, Names())
+    assert set(t) == {"e", "L3.mixer.inner.gate.weight", "fn.weight"}
+    with pytest.raises(KeyError):
+        tensor_table({"layers/3/mixer": ParamSpec((2, 2))}, Names())
+    with pytest.raises(KeyError):
+        tensor_table({"positions": ParamSpec((2, 2))}, Names())       # a position table without a name for it
