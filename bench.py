@@ -33,7 +33,12 @@ PHI2 = dict(architectures=["PhiForCausalLM"], model_type="phi", num_hidden_layer
 # Phi-1.5 sizes (Phi-1 has the same layer shapes)
 PHI15 = dict(PHI2, num_hidden_layers=24, hidden_size=2048, intermediate_size=8192, partial_rotary_factor=0.5)
 MODELS = {"phi-2": ("Phi-2", PHI2, 2), "phi-1.5": ("Phi-1.5", PHI15, 3)}      # label, sizes, seed of the weights
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# Untimed decode steps between the prompts and the warm-up, the same whatever --warmup says.  After the
+# prompts' products, which run at the power limit, the SM clock comes back in stages over about 35
+# decode steps (90 ms; 3.05, 2.89, 2.68, 2.52, then 2.45 ms a step were measured): without them a figure
+# would depend on how long ago the prompts ran, which is to say on the caller's --warmup.
+SETTLE_STEPS = 40
 
 
 def peaks():
@@ -42,7 +47,8 @@ def peaks():
         try:
             with open(path) as f:
                 p = json.load(f)
-            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained") or 0.0)}, "measured"
         except Exception:
             pass
     return dict(FALLBACK_PEAKS), "fallback"
@@ -141,6 +147,7 @@ def main():
     if args.ragged:
         return ragged(args, label, cfg, weight_seed, layers, layers_full)
     K, W, B, C = args.steps, args.warmup, args.batch, args.context
+    S = SETTLE_STEPS
     max_b = max(B, 64) if "points" in sections else B
     model = gl.load_random(cfg, seed=weight_seed, dtype="bfloat16", max_tokens=max_b * C, layers=layers)
     eng = model.engine
@@ -148,77 +155,117 @@ def main():
     rng = np.random.default_rng(4)
     V = spec.vocab
     greedy = SamplerConfig.greedy()
+    greedy_kw = dict(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0, stop_tokens=(), seed=5)
+    # bytes a decode step has to read: every matrix it uses once (the embedding table is only gathered
+    # from) and the cached keys and values of the live sequences
     weight_bytes = sum(t.numel() * t.element_size() for t in eng.model._all_tensors()
                        if t is not None and t.dim() == 2) - eng.model.embedding.numel() * eng.model.embedding.element_size()
     kv_per_pos = eng.cache.bytes_per_position()
 
-    def decode_rate(batch, steps, warmup, context):
-        """tokens a second of `steps` on-device decode steps ending at `context` positions."""
-        prompt_len = context - steps - warmup - 1
-        prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(batch)]
+    def decode_rate(batch, steps, warmup, context, prompts=None, S=S):
+        """`steps` on-device decode steps that end at `context` positions, after the prompts, S settling
+        steps and `warmup` steps.  Returns tokens a second, ms a step, the mean cached length over the timed
+        steps, and every token chosen after the prompts (the first from the prompts' logits)."""
+        prompt_len = context - steps - warmup - S - 1
+        if prompt_len < 1:
+            raise SystemExit(f"context {context} is too short for {steps} + {warmup} + {S} steps")
+        if prompts is None:
+            prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(batch)]
         slots = [eng.open() for _ in range(batch)]
         sampler = DeviceSampler(greedy, [request_seed(5, i) for i in range(batch)], prompts, V, eng.device)
+        first = []
         for i in range(0, batch, 8):                       # fill the cache, 8 prompts a step
-            logits = eng.step([(slots[j], prompts[j]) for j in range(i, min(batch, i + 8))])
-        first = [int(t) for t in rng.integers(0, V, size=batch)]
-        eng.decode_loop(slots, first, 1, sampler)          # captures the step
+            rows = list(range(i, min(batch, i + 8)))
+            logits = eng.step([(slots[j], prompts[j]) for j in rows])
+            first += sampler.sample(logits, torch.tensor(rows, dtype=torch.int32).to(eng.device)).tolist()
+        chosen = [first]
+        toks = eng.decode_loop(slots, first, 1, sampler)   # captures the step
+        chosen += toks.tolist()
         ops.LAUNCHES = 0
-        toks = eng.decode_loop(slots, first, warmup, sampler)
+        if S + warmup > 1:
+            toks = eng.decode_loop(slots, toks[-1].tolist(), S + warmup - 1, sampler)
+            chosen += toks.tolist()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         toks = eng.decode_loop(slots, toks[-1].tolist(), steps, sampler)
         e1.record()
         torch.cuda.synchronize()
+        eng.check_device()
+        chosen += toks.tolist()
         ms = e0.elapsed_time(e1)
         ctx_mid = context - 1 - steps / 2.0
         for s in slots:
             eng.close(s)
-        return batch * steps / (ms / 1e3), ms / steps, ctx_mid
+        return batch * steps / (ms / 1e3), ms / steps, ctx_mid, chosen
 
-    value, ms_step, ctx_mid, clock_info, launches_per_step = 0.0, float("nan"), C - 1 - K / 2.0, {}, 0
+    def point(batch, steps, context, settle_elsewhere=False):
+        """One more decode measurement as a record: rate, time, bytes and the fraction of the HBM peak.
+        ``settle_elsewhere``: the settling steps run on sequences of their own first, for a context too
+        short to hold them."""
+        if settle_elsewhere:
+            decode_rate(batch, 1, 1, 8 + S + 3, S=S)
+            rate, ms, mid, _ = decode_rate(batch, steps, 3, context, S=0)
+        else:
+            rate, ms, mid, _ = decode_rate(batch, steps, W, context)
+        nbytes = weight_bytes + batch * mid * kv_per_pos
+        return {"value": round(rate, 1), "ms_per_step": round(ms, 4), "batch": batch, "context": context,
+                "bytes": int(nbytes), "frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                "weights_only_frac": round(weight_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+
+    prompt_len = C - K - W - S - 1
+    prompts = [[int(t) for t in rng.integers(0, V, size=max(1, prompt_len))] for _ in range(B)]
+    value, ms_step, ctx_mid, clock_info, launches_per_step, loop_tokens = 0.0, float("nan"), C - 1 - K / 2.0, {}, 0, None
     if "decode" in sections:
         clocks = ClockSampler()
         clocks.start()
-        value, ms_step, ctx_mid = decode_rate(B, K, W, C)
+        value, ms_step, ctx_mid, loop_tokens = decode_rate(B, K, W, C, prompts)
         clock_info = clocks.stop()
         launches_per_step = eng.launches_per_loop_step.get(B, 0)
 
     # the same work through the Python entry point: host tokens in, host tokens out
     e2e = None
+    same_tokens = None
     if "e2e" in sections:
-        prompt_len = C - K - W - 1
-        prompts = [[int(t) for t in rng.integers(0, V, size=prompt_len)] for _ in range(B)]
-        model.generate(prompts[:B], max_tokens=4, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
-                       stop_tokens=(), seed=5)             # warm-up: captures the decode step for this batch
-        res = model.generate(prompts, max_tokens=K + W, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
-                             stop_tokens=(), seed=5)
-        # the W tokens after the prompt are warm-up, as in the device-timed loop: the last K count
+        model.generate(prompts, max_tokens=4, **greedy_kw)     # warm-up: captures the decode step for this batch
+        res = model.generate(prompts, max_tokens=1 + S + W + K, **greedy_kw)
+        # the S + W tokens after the prompt settle and warm up, as in the device-timed loop: the last K count
         dec_s = max(r.stats.token_times[-1] - (r.stats.token_times[-1 - K] if len(r.stats.token_times) > K
                                                  else r.stats.prefill_time) for r in res)
         e2e_value = B * K / dec_s
         e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": eng.h2d_bytes_last + 4 * B,
                "d2h_bytes_per_step": 4 * B}
+        if loop_tokens is not None:
+            # both figures come from one computation: the device loop chose the tokens the entry point chose
+            n = min(len(loop_tokens), min(len(r.tokens) for r in res))
+            same_tokens = all([row[i] for row in loop_tokens[:n]] == r.tokens[:n] for i, r in enumerate(res))
+            if not same_tokens:
+                raise SystemExit("bench: the on-device decode loop and Model.generate chose different tokens "
+                                 "for the same prompts")
+            e2e["same_tokens_as_device_loop"] = n
 
     step_bytes = weight_bytes + B * ctx_mid * kv_per_pos
     achieved = step_bytes / (ms_step / 1e3) / 1e9 if "decode" in sections else 0.0
+    head_dim = spec.layers[0].mixer.head_dim
     out = {
         "metric": f"decode tok/s at batch {B}, context {C} ({label} sizes, bf16)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4) if "decode" in sections else None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": f"synthetic: random weights N(0,0.02) seed {weight_seed}, token ids uniform in [0,51200)",
         "config": {"model": f"{label} sizes (PhiForCausalLM)", "layers": layers, "layers_of_model": layers_full,
-                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"],
-                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "rotary_dim": int(cfg["partial_rotary_factor"] * (cfg["hidden_size"] // cfg["num_attention_heads"])),
+                   "hidden": spec.hidden, "heads": spec.layers[0].mixer.num_heads,
+                   "kv_heads": spec.layers[0].mixer.num_kv_heads, "head_dim": head_dim,
+                   "intermediate": spec.layers[0].ffn.intermediate, "vocab": spec.vocab,
+                   "rotary_dim": spec.layers[0].mixer.position.rotary_dim,
                    "global_batch": B, "seq_len": C,
-                   "context_at_timed_steps": f"{C - K - 1}..{C - 1}", "parallelism": "single GPU",
+                   "context_at_timed_steps": f"{C - K - 1}..{C - 1}", "settle_steps": S, "parallelism": "single GPU",
                    "sampling": "greedy", "l2": "each step reads weights and cache far larger than L2 (126 MB)",
                    "peaks": pk_src},
         "clocks": clock_info, "e2e": e2e, "gpu_launches": launches_per_step * K,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes": int(step_bytes),
+                     "weights_only_frac": round(weight_bytes / (ms_step / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+                     if "decode" in sections else None},
     }
     if "prefill" in sections:
         T = 2048
@@ -237,15 +284,20 @@ def main():
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
             eng.close(s)
+        eng.check_device()
         ms = min(times)
         layer_params = sum(w.numel() for e in spec.schedule for _, w, _, _ in eng.model.blocks[e.layer].products())
-        flops = 2.0 * T * layer_params + 2.0 * T * T * cfg["hidden_size"] * layers + 2.0 * V * cfg["hidden_size"]
+        flops = 2.0 * T * layer_params + 2.0 * T * T * spec.hidden * len(spec.schedule) + 2.0 * V * spec.hidden
         out["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
-                          "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+                          "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                          "peak": "bf16_tflops (a burst of one product)", "flops": flops,
+                          "frac_sustained": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
+                          if pk.get("bf16_tflops_sustained") else None}
     if "points" in sections:
-        b1, _, _ = decode_rate(1, min(K, 64), W, C)
-        b64, _, _ = decode_rate(64, min(K, 32), W, C)
-        out["points"] = {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1)}
+        detail = {"decode_b1": point(1, min(K, 64), C), "decode_b64": point(64, min(K, 32), C),
+                  "decode_b64_ctx128": point(64, 16, 128, settle_elsewhere=True)}
+        out["points"] = {"decode_b1": detail["decode_b1"]["value"], "decode_b64": detail["decode_b64"]["value"]}
+        out["points_detail"] = detail
     print(json.dumps(out))
     return 0
 

@@ -8,9 +8,10 @@ GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu",
            "sampling.cu")
 
 # libraries compiled once per head size (GL_HEAD_DIM)
-PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu")
+PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",
+                                  "decode_layer.cu")
 # libraries that take only some head sizes
-MAX_HEAD_DIM = {"attention_prefill_tc.cu": 128}
+MAX_HEAD_DIM = {"attention_prefill_tc.cu": 128, "decode_layer.cu": 128}
 
 
 def head_dim_defines(head_dim: int) -> Tuple[str, ...]:

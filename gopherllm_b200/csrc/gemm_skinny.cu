@@ -114,22 +114,28 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
         __syncthreads();                                      // everyone is done with the stage refilled next
         if (tid == 0 && it + STAGES - 1 < iters) { load_w(it + STAGES - 1); load_a(it + STAGES - 1); }
         const unsigned sb = base + (it % STAGES) * STAGE;
+        // a stage's fragments are asked for ahead of the products that need them (the weights' for the
+        // whole stage, the tokens' for a k-step at a time): a warp that loaded and multiplied in turn
+        // would wait out a shared-memory round trip before every product
+        unsigned af[SK_BK / 16][4];
 #pragma unroll
         for (int kk = 0; kk < SK_BK / 16; ++kk) {
-            unsigned a0, a1, a2, a3;
-            {
-                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                const int c = kk * 2 + (lane >> 4);
-                ldmatrix_x4(sb + swz(r, c), a0, a1, a2, a3);
-            }
+            const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int c = kk * 2 + (lane >> 4);
+            ldmatrix_x4(sb + swz(r, c), af[kk][0], af[kk][1], af[kk][2], af[kk][3]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < SK_BK / 16; ++kk) {
+            unsigned bf[MT][2];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                unsigned b0, b1;
                 const int r = mt * 8 + (lane & 7);
                 const int c = kk * 2 + ((lane >> 3) & 1);
-                ldmatrix_x2(sb + W_BYTES + swz(r, c), b0, b1);
-                mma_bf16(acc[mt], a0, a1, a2, a3, b0, b1);
+                ldmatrix_x2(sb + W_BYTES + swz(r, c), bf[mt][0], bf[mt][1]);
             }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                mma_bf16(acc[mt], af[kk][0], af[kk][1], af[kk][2], af[kk][3], bf[mt][0], bf[mt][1]);
         }
     }
     __syncthreads();

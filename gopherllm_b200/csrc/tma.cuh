@@ -119,7 +119,9 @@ GL_API int gl_wait_status(int clear) {
     return v;
 }
 
+#ifndef GL_SPIN_LIMIT
 #define GL_SPIN_LIMIT (1u << 22)      // tries before a wait gives up (each try may itself sleep briefly)
+#endif
 
 __device__ __forceinline__ unsigned gl_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 

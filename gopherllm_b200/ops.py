@@ -458,6 +458,125 @@ def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads
                       num_heads, num_kv_heads, head_dim, ctx.max_qlen, window)
 
 
+class _DecodeLayerArgs(Structure):
+    _fields_ = [("x", c_void_p), ("norm_g", c_void_p), ("norm_b", c_void_p),
+                ("w_qkv", c_void_p), ("b_qkv", c_void_p), ("w_up", c_void_p), ("b_up", c_void_p),
+                ("w_out", c_void_p), ("b_out", c_void_p), ("w_down", c_void_p), ("b_down", c_void_p),
+                ("k_cache", c_void_p), ("v_cache", c_void_p), ("pages", c_void_p), ("seq_ctx", c_void_p),
+                ("cosv", c_void_p), ("sinv", c_void_p),
+                ("xn", c_void_p), ("qkv", c_void_p), ("o", c_void_p), ("h", c_void_p),
+                ("scratch", c_void_p), ("sync", c_void_p),
+                ("M", c_int), ("D", c_int), ("I", c_int), ("nH", c_int), ("nKV", c_int), ("half", c_int),
+                ("max_pages", c_int), ("n_pages", c_int), ("window", c_int), ("act", c_int), ("rms", c_int),
+                ("write_kv", c_int), ("eps", c_float), ("q_scale", c_float)]
+
+
+DECODE_LAYER_MAX_ROWS = 64
+# Fewer tokens than this go through the separate kernels, which are faster there (measured on Phi-2's
+# sizes: 10 to 20 % at 1 to 16 tokens, equal at 32, the fused layer 3 to 6 % ahead at 48 and 64).
+DECODE_LAYER_MIN_ROWS = 33
+DECODE_LAYER_MAX_HEAD_DIM = catalog.MAX_HEAD_DIM["decode_layer.cu"]
+USE_DECODE_LAYER = True
+_DECODE_LAYER_KEEP = None          # a dict here receives the work buffers of the last call (for tests)
+_DECODE_LAYER_SYNC: dict = {}      # device index -> the int32 words the fused layer's blocks meet through
+
+
+def decode_layer_takes(x, w_qkv, w_up, w_out, w_down, cache_dtype, head_dim: int, group: int, rotary_half: int,
+                       interleaved: bool, head_norm: bool) -> bool:
+    """Whether the fused decode layer takes these types and sizes (the caller falls back to the separate
+    kernels otherwise): bfloat16 weights and cache, DECODE_LAYER_MIN_ROWS to 64 tokens, head sizes up to 128 in steps of 16,
+    up to 8 query heads per key/value head, split-half rotation over a multiple of 16 dims, no per-head
+    norm, widths that are multiples of 8."""
+    return (USE_DECODE_LAYER and DECODE_LAYER_MIN_ROWS <= x.shape[0] <= DECODE_LAYER_MAX_ROWS
+            and cache_dtype == torch.bfloat16
+            and all(w.dtype == torch.bfloat16 for w in (w_qkv, w_up, w_out, w_down))
+            and head_dim % 16 == 0 and head_dim <= DECODE_LAYER_MAX_HEAD_DIM and group <= DECODE_MAX_GROUP
+            and rotary_half % 8 == 0 and not interleaved and not head_norm
+            and x.shape[1] % 8 == 0 and w_up.shape[0] % 8 == 0 and w_out.shape[1] % 8 == 0)
+
+
+def decode_layer(x: torch.Tensor, norm_g: torch.Tensor, norm_b: Optional[torch.Tensor], eps: float, rms: bool,
+                 w_qkv: torch.Tensor, b_qkv, w_up: torch.Tensor, b_up, act, w_out: torch.Tensor, b_out,
+                 w_down: torch.Tensor, b_down, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 seq_ctx: torch.Tensor, pages: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                 q_scale: float, cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                 window: int = 0, write_kv: bool = True) -> torch.Tensor:
+    """One decode step of a parallel block in one kernel, x updated in place:
+    n = norm(x); x += attention(n) · w_outᵀ + b_out + act(n · w_upᵀ + b_up) · w_downᵀ + b_down, with one
+    token per sequence (row b of x is sequence b's new token at position seq_ctx[b]); the new token's
+    rotated key and its value go into the cache (write_kv).  All calls on a device share a few words of
+    synchronisation state: they must follow one another on a stream, never overlap."""
+    M, D = x.shape
+    _need(x, "x", torch.float32)
+    _need(norm_g, "norm weight", torch.float32, (D,))
+    if norm_b is not None:
+        _need(norm_b, "norm bias", torch.float32, (D,))
+    Nqkv, No, I = (num_heads + 2 * num_kv_heads) * head_dim, num_heads * head_dim, w_up.shape[0]
+    _need(w_qkv, "w_qkv", torch.bfloat16, (Nqkv, D))
+    _need(w_up, "w_up", torch.bfloat16, (I, D))
+    _need(w_out, "w_out", torch.bfloat16, (D, No))
+    _need(w_down, "w_down", torch.bfloat16, (D, I))
+    for n, b, k in (("b_qkv", b_qkv, Nqkv), ("b_up", b_up, I), ("b_out", b_out, D), ("b_down", b_down, D)):
+        if b is not None:
+            _need(b, n, torch.float32, (k,))
+    _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
+    if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
+        raise KernelError(f"cache pages must be [*, {num_kv_heads}, {PAGE}, {head_dim}], are {tuple(k_cache.shape)}")
+    _need(seq_ctx, "seq_ctx", torch.int32, (M,))
+    _need(pages, "pages", torch.int32)
+    if pages.shape[0] != M:
+        raise KernelError(f"pages has {pages.shape[0]} rows for {M} sequences")
+    half = 0
+    if cos is not None:
+        _need(cos, "cos", torch.float32)
+        _need(sin, "sin", torch.float32, cos.shape)
+        half = cos.shape[1]
+        if cos.shape[0] != M:
+            raise KernelError(f"rotary tables {tuple(cos.shape)} do not fit {M} tokens")
+    if act not in ACTIVATIONS:
+        raise KernelError(f"activation {act!r} unknown")
+    if M > DECODE_LAYER_MAX_ROWS or head_dim % 16 or head_dim > DECODE_LAYER_MAX_HEAD_DIM:
+        raise KernelError(f"the fused decode layer takes up to {DECODE_LAYER_MAX_ROWS} tokens and head sizes up to "
+                          f"{DECODE_LAYER_MAX_HEAD_DIM} in steps of 16")
+    dev = x.device
+    lib = _lib("decode_layer.cu", catalog.head_dim_defines(head_dim))
+    bf = torch.bfloat16
+    xn = torch.empty((M, D), dtype=bf, device=dev)
+    qkv = torch.empty((M, Nqkv), dtype=bf, device=dev)
+    o = torch.empty((M, No), dtype=bf, device=dev)
+    h = torch.empty((M, I), dtype=bf, device=dev)
+    a = _DecodeLayerArgs(x.data_ptr(), norm_g.data_ptr(), _addr(norm_b), w_qkv.data_ptr(), _addr(b_qkv),
+                         w_up.data_ptr(), _addr(b_up), w_out.data_ptr(), _addr(b_out), w_down.data_ptr(), _addr(b_down),
+                         k_cache.data_ptr(), v_cache.data_ptr(), pages.data_ptr(), seq_ctx.data_ptr(),
+                         _addr(cos), _addr(sin), xn.data_ptr(), qkv.data_ptr(), o.data_ptr(), h.data_ptr(), None, None,
+                         M, D, I, num_heads, num_kv_heads, half, pages.shape[-1], k_cache.shape[0], window,
+                         ACTIVATIONS[act], 1 if rms else 0, 1 if write_kv else 0, eps, q_scale)
+    n_scratch, n_sync = ctypes.c_longlong(0), ctypes.c_longlong(0)
+    _check(lib.gl_decode_layer_sizes(byref(a), byref(n_scratch), byref(n_sync)), "decode_layer", 0)
+    idx = dev.index or 0
+    sync = _DECODE_LAYER_SYNC.get(idx)
+    if sync is None or sync.numel() < n_sync.value:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the fused decode layer's synchronisation words must exist before a capture: "
+                              "run the step once outside it")
+        # zero once; every call leaves the counters zero again (the generation word only ever grows)
+        sync = _DECODE_LAYER_SYNC[idx] = torch.zeros(max(int(n_sync.value), 1 << 16), dtype=torch.int32, device=dev)
+    scratch = torch.empty(max(1, int(n_scratch.value)), dtype=torch.float32, device=dev)
+    a.scratch, a.sync = scratch.data_ptr(), sync.data_ptr()
+    _check(lib.gl_decode_layer(byref(a), _stream()), "decode_layer")
+    if _DECODE_LAYER_KEEP is not None:
+        _DECODE_LAYER_KEEP.update(xn=xn, qkv=qkv, o=o, h=h)
+    return x
+
+
+def reset_decode_layer_sync() -> None:
+    """Zero the fused decode layer's synchronisation words (after a kernel gave up a wait mid-way they
+    may be left counting)."""
+    for t in _DECODE_LAYER_SYNC.values():
+        t.zero_()
+
+
 class _GemmArgs(Structure):
     _fields_ = [("a", c_void_p), ("w", c_void_p), ("bias", c_void_p), ("add0", c_void_p),
                 ("add1", c_void_p), ("out", c_void_p),
@@ -600,6 +719,7 @@ def check_wait_failures() -> None:
     check; the words are cleared, so the next check speaks of what ran after this one."""
     bad = sorted(k for k, v in wait_failures(clear=True).items() if v != 0)
     if bad:
+        reset_decode_layer_sync()
         raise KernelError("a kernel gave up waiting (for a TMA copy or a tensor-core product) in "
                           + ", ".join(bad) + ": the results since the last check are invalid")
 

@@ -81,6 +81,18 @@ class Attention(Mixer):
     def products(self):
         return [("qkv", self.w_qkv, self.b_qkv, None), ("out", self.w_out, self.b_out, None)]
 
+    def decode_fusable(self, ctx, cache):
+        if not ctx.is_decode or cache is None:
+            return None
+        s = self.spec
+        tables = self.position.tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        return dict(w_qkv=self.w_qkv, b_qkv=self.b_qkv, w_out=self.w_out, b_out=self.b_out,
+                    num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, q_scale=s.q_scale,
+                    window=s.window, cos=cos, sin=sin, interleaved=s.position.interleaved,
+                    head_norm=self.q_norm is not None, k=cache.k, v=cache.v, pages=ctx.pages[cache.group],
+                    writes=cache.writes)
+
     def until_last(self, xn, ctx, cache, first=None):
         """Everything but the output projection: the attention output [T, heads * head size] with the
         projection's weight and bias.  ``first``: the joined q, k, v projection if the caller made it."""

@@ -75,7 +75,10 @@ class Part:
 
 
 class Norm(Part):
-    """forward(x float32 [R, D], out_dtype, rows=None) -> [R', D] of out_dtype."""
+    """forward(x float32 [R, D], out_dtype, rows=None) -> [R', D] of out_dtype.
+    Optional: ``fusable()`` -> (weight, bias or None, eps, rms) for a block that runs its decode step
+    as one kernel; a norm without it is simply run through ``forward``."""
+    fusable = None
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
@@ -110,6 +113,12 @@ class Mixer(Part):
     # computing it, so that a block can run the first products of its branches as one (ops.linear_fork).
     first_product = None
 
+    # Optional: ``decode_fusable(ctx, cache)`` -> a dict describing a one-token-a-sequence step of softmax
+    # attention over the paged cache (w_qkv, b_qkv, w_out, b_out, num_heads, num_kv_heads, head_dim, q_scale,
+    # window, cos, sin, interleaved, head_norm, k, v, pages, writes), or None when this step is not of
+    # that kind; a block whose parts all offer the fused form may run its decode step as one kernel.
+    decode_fusable = None
+
     # A mixer that sets this accepts callables among ``add``: it calls them just before its last
     # product and adds what they return.  A block uses that to let another branch run beside the
     # mixer on a second stream and join only where its result is needed.
@@ -126,6 +135,8 @@ class FeedForward(Part):
 
     until_last = None
     first_product = None
+    # Optional: ``fusable()`` -> (w_up, b_up, activation, w_down, b_down) of a plain two-product feed-forward.
+    fusable = None
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

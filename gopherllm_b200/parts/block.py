@@ -57,7 +57,30 @@ class ParallelBlock(AssembledBlock):
     (model.go:2738-2740) and both are added to the residual, the feed-forward
     first (model.go:2812-2815)."""
 
+    def _decode_step_as_one_kernel(self, x, ctx, cache) -> bool:
+        """With one token a sequence a layer is a stream of weights and cached keys and values; where
+        every part offers its fused form and the kernel takes the sizes, the whole block runs as one
+        persistent kernel that keeps that stream going from the norm to the residual sum."""
+        if not (ctx.is_decode and ctx.act_dtype == torch.bfloat16 and self.norm.fusable is not None
+                and self.mixer.decode_fusable is not None and self.ffn.fusable is not None):
+            return False
+        m = self.mixer.decode_fusable(ctx, cache)
+        if m is None:
+            return False
+        w_up, b_up, act, w_down, b_down = self.ffn.fusable()
+        half = 0 if m["cos"] is None else m["cos"].shape[1]
+        if not ops.decode_layer_takes(x, m["w_qkv"], w_up, m["w_out"], w_down, m["k"].dtype, m["head_dim"],
+                                      m["num_heads"] // m["num_kv_heads"], half, m["interleaved"], m["head_norm"]):
+            return False
+        g, b, eps, rms = self.norm.fusable()
+        ops.decode_layer(x, g, b, eps, rms, m["w_qkv"], m["b_qkv"], w_up, b_up, act, m["w_out"], m["b_out"],
+                         w_down, b_down, m["k"], m["v"], ctx.seq_ctx, m["pages"], m["num_heads"], m["num_kv_heads"],
+                         m["head_dim"], m["q_scale"], m["cos"], m["sin"], m["window"], m["writes"])
+        return True
+
     def forward(self, x, ctx, cache):
+        if self._decode_step_as_one_kernel(x, ctx, cache):
+            return x
         xn = self.norm.forward(x, ctx.act_dtype)
         side = getattr(ctx, "side_stream", None)
         if self.ffn.until_last is not None and self.mixer.until_last is not None:

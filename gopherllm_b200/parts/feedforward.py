@@ -38,6 +38,9 @@ class DenseFeedForward(FeedForward):
     def first_product(self):
         return self.w_up, self.b_up, self.spec.activation
 
+    def fusable(self):
+        return self.w_up, self.b_up, self.spec.activation, self.w_down, self.b_down
+
     def products(self):
         return [("up", self.w_up, self.b_up, self.spec.activation), ("down", self.w_down, self.b_down, None)]
 

@@ -31,6 +31,9 @@ class LayerNorm(Norm):
         self.weight = tensors["weight"]
         self.bias = tensors.get("bias")
 
+    def fusable(self):
+        return self.weight, self.bias, self.spec.eps, self.rms
+
     def forward(self, x, out_dtype, rows=None):
         return ops.norm(x, self.weight, self.bias, self.spec.eps, out_dtype, rms=self.rms, rows=rows)
 

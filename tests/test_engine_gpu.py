@@ -238,3 +238,106 @@ def test_captured_steps_are_kept_up_to_a_limit():
         eng.graph_limit = old
         eng._graphs.update(kept)
     eng.cache.check()
+
+
+@pytest.fixture
+def fused_layer_for_any_batch():
+    """The fused decode layer is taken for more than 32 tokens by default; these tests want it from one."""
+    from gopherllm_b200 import ops
+    old = ops.DECODE_LAYER_MIN_ROWS
+    ops.DECODE_LAYER_MIN_ROWS = 1
+    yield ops
+    ops.DECODE_LAYER_MIN_ROWS = old
+
+
+def test_fused_decode_layer_whole_then_one_by_one(fused_layer_for_any_batch):
+    """Configuration D through the fused decode layer (forced on for single tokens, steps run kernel by
+    kernel and from captured graphs): a prompt, then 60 tokens one by one across a page's edge; and
+    the same steps through the separate kernels agree with it within rounding."""
+    import gopherllm_b200 as gl
+    ops = fused_layer_for_any_batch
+    cfg = tiny.TINY["D"][0]
+    rng = np.random.default_rng(17)
+    toks = tiny.prompt(rng, 200, cfg["vocab_size"])
+    ref = plain_logits("D", toks)
+    m = gl.load(tiny.folder("D"), dtype="bfloat16", max_tokens=1024)
+    launched = []
+    real = ops.decode_layer
+    ops.decode_layer = lambda *a, **k: (launched.append(a[0].shape[0]), real(*a, **k))[1]
+    try:
+        s = m.open_sequence()
+        got = [m.step([(s, toks[:140])], [list(range(140))]).cpu().numpy()]
+        for t in range(140, 200):
+            got.append(m.step([(s, [toks[t]])]).cpu().numpy())
+        m.close_sequence(s)
+    finally:
+        ops.decode_layer = real
+    assert launched and set(launched) == {1}, "the decode steps did not go through the fused layer"
+    got = np.concatenate(got)
+    for t in range(200):
+        err, bound = tiny.close(got[t], ref[t], "bfloat16")
+        assert err <= bound, f"first wrong position {t}: {err:.3e} > {bound:.3e}"
+    m.engine.check_device()
+    m.close()
+
+
+def test_fused_decode_layer_unequal_batches(fused_layer_for_any_batch):
+    """Unequal prompts in one step, then one token each through the fused layer; shorter requests end
+    earlier; a second batch reuses their slots and pages."""
+    import gopherllm_b200 as gl
+    cfg = tiny.TINY["D"][0]
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(18)
+    m = gl.load(tiny.folder("D"), dtype="bfloat16", max_tokens=2048)
+    cache = m.engine.cache
+    for lens, decs in (([250, 5, 64, 17, 130], [40, 3, 9, 1, 66]), ([3, 65, 1], [30, 12, 5])):
+        seqs = [tiny.prompt(rng, a + d, V) for a, d in zip(lens, decs)]
+        refs = [plain_logits("D", s) for s in seqs]
+        slots = [m.open_sequence() for _ in seqs]
+        m.step([(slots[i], seqs[i][:lens[i]]) for i in range(len(seqs))], [[] for _ in seqs])
+        live = list(range(len(seqs)))
+        for step in range(max(decs)):
+            live = [i for i in live if step < decs[i]]
+            out = m.step([(slots[i], [seqs[i][lens[i] + step]]) for i in live]).cpu().numpy()
+            for r, i in enumerate(live):
+                err, bound = tiny.close(out[r], refs[i][lens[i] + step], "bfloat16")
+                assert err <= bound, f"batch {lens}: request {i} wrong at position {lens[i] + step}: {err:.3e} > {bound:.3e}"
+                if step + 1 == decs[i]:
+                    m.close_sequence(slots[i])
+        cache.check()
+        assert cache.slots.held_count == 0 and all(g.pool.held_count == 0 for g in cache.groups)
+    m.engine.check_device()
+    m.close()
+
+
+def test_forty_sequences_take_the_fused_decode_layer_by_default():
+    """More than 32 tokens a step go through the fused layer without being asked to: 40 sequences of
+    unequal lengths, three steps, every row against the plain implementation."""
+    import gopherllm_b200 as gl
+    from gopherllm_b200 import ops
+    cfg = tiny.TINY["D"][0]
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(19)
+    m = gl.load(tiny.folder("D"), dtype="bfloat16", max_tokens=40 * 128)
+    lens = [int(n) for n in rng.integers(1, 100, size=40)]
+    seqs = [tiny.prompt(rng, n + 3, V) for n in lens]
+    slots = [m.open_sequence() for _ in seqs]
+    launched = []
+    real = ops.decode_layer
+    ops.decode_layer = lambda *a, **k: (launched.append(a[0].shape[0]), real(*a, **k))[1]
+    try:
+        for i in range(0, 40, 8):
+            m.step([(slots[j], seqs[j][:lens[j]]) for j in range(i, i + 8)], [[] for _ in range(8)])
+        outs = [m.step([(slots[i], [seqs[i][lens[i] + step]]) for i in range(40)]).cpu().numpy() for step in range(3)]
+    finally:
+        ops.decode_layer = real
+    assert launched and set(launched) == {40}
+    for i in range(0, 40, 3):
+        ref = plain_logits("D", seqs[i])
+        for step in range(3):
+            err, bound = tiny.close(outs[step][i], ref[lens[i] + step], "bfloat16")
+            assert err <= bound, (i, step, err, bound)
+    for s in slots:
+        m.close_sequence(s)
+    m.engine.cache.check()
+    m.close()

@@ -603,3 +603,86 @@ def test_sampling_matches_plain(V):
                     want = g_
                 assert got[d][i] == want, (ci, i, d, got[d][i], want)
                 rec = (rec + [want])[-64:]
+
+
+# --------------------------------------------------------------------------
+# the fused decode layer: one kernel for norm, both branches and the residual sum
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("M,nH,nKV,hd,D,I,rot,window,rms,act,bias", [
+    (5, 4, 4, 64, 256, 328, 32, 0, False, "gelu_new", True),      # a page's edge, an empty cache, several pages
+    (40, 8, 2, 32, 264, 520, 16, 100, True, "relu", False),       # grouped heads, a window, no biases, 40 tokens
+    (64, 2, 1, 128, 256, 256, 0, 0, False, "gelu", True),         # the largest head and batch, no rotation
+    (17, 6, 3, 48, 288, 200, 48, 0, False, "gelu_new", True),     # head size 48, a fully rotated head
+    (1, 32, 32, 80, 2560, 10240, 32, 0, False, "gelu_new", True), # one token at Phi-2's sizes
+])
+def test_decode_layer(M, nH, nKV, hd, D, I, rot, window, rms, act, bias):
+    """norm -> (attention over the paged cache | feed-forward) -> residual sum as one kernel, against the
+    same layer written out in 64-bit: the residual stream, and the cache (the new token's rotated key and
+    its value where they belong, everything else, NaN filling included, untouched)."""
+    o = ops()
+    rng = np.random.default_rng(M + hd)
+    ctxs = [0, 63, 64, 200, 129][:M] if M <= 5 else [int(c) for c in rng.integers(0, 300, size=M)]
+    dtype = torch.bfloat16
+    L = max(ctxs) + 1
+    k = rnd(M, L, nKV, hd, seed=1).to(dtype).float()
+    v = rnd(M, L, nKV, hd, seed=2).to(dtype).float()
+    kc, vc, table = make_cache(k, v, [c + 1 for c in ctxs], dtype, seed=3)
+    for b, c in enumerate(ctxs):                               # the new token's row is not there yet
+        page = int(table[b, c // PAGE])
+        kc[page, :, c % PAGE] = float("nan")
+        vc[page, :, c % PAGE] = float("nan")
+    kc0, vc0 = kc.clone(), vc.clone()
+    i32 = lambda t: torch.tensor(np.asarray(t), dtype=torch.int32, device=DEV)
+    Nqkv, No = (nH + 2 * nKV) * hd, nH * hd
+    x = rnd(M, D, seed=4)
+    g, b_ = 1 + rnd(D, scale=0.1, seed=5), (rnd(D, scale=0.1, seed=6) if not rms else None)
+    s = 1.0 / math.sqrt(D)
+    w_qkv, w_up = rnd(Nqkv, D, scale=s, seed=7).to(dtype), rnd(I, D, scale=s, seed=8).to(dtype)
+    w_out, w_down = rnd(D, No, scale=1 / math.sqrt(No), seed=9).to(dtype), rnd(D, I, scale=1 / math.sqrt(I), seed=10).to(dtype)
+    bq, bu, bo, bd = ((rnd(n, scale=0.1, seed=11 + i) for i, n in enumerate((Nqkv, I, D, D))) if bias else (None,) * 4)
+    cos = sin = None
+    if rot:
+        from gopherllm_b200.parts.position import rope_inverse_frequencies
+        cos, sin = o.rope_table(i32(ctxs), torch.from_numpy(rope_inverse_frequencies(rot, 10000.0)).to(DEV))
+    scale = 1.0 / math.sqrt(hd)
+    x0 = x.clone()
+    o.decode_layer(x, g, b_, 1e-5, rms, w_qkv, bq, w_up, bu, act, w_out, bo, w_down, bd, kc, vc, i32(ctxs), table,
+                   nH, nKV, hd, scale, cos, sin, window, True)
+    torch.cuda.synchronize()
+    assert all(val == 0 for val in o.wait_failures().values()), "a bounded wait ran out"
+    # the same layer in 64-bit, rounding to bfloat16 where the kernel's buffers do
+    r16 = lambda t: t.to(dtype).double()
+    xd = x0.double().cpu()
+    if rms:
+        n = xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5) * g.double().cpu()
+    else:
+        n = plain_phi.layer_norm(xd, g.double().cpu(), b_.double().cpu(), 1e-5)
+    n = r16(n)
+    z = lambda t, m: t.double().cpu() if t is not None else torch.zeros(m, dtype=torch.float64)
+    qkv = r16(n @ w_qkv.double().cpu().T + z(bq, Nqkv))
+    h = r16(gelu_ref(n @ w_up.double().cpu().T + z(bu, I), act))
+    q, kn, vn = qkv[:, :No].reshape(M, nH, hd), qkv[:, No:No + nKV * hd].reshape(M, nKV, hd), qkv[:, No + nKV * hd:].reshape(M, nKV, hd)
+    if rot:
+        q = plain_phi.apply_rope(q, sin.double().cpu(), cos.double().cpu(), rot)
+        kn = plain_phi.apply_rope(kn, sin.double().cpu(), cos.double().cpu(), rot)
+    q, kn = r16(q * scale), r16(kn)
+    att = torch.zeros(M, nH, hd, dtype=torch.float64)
+    for b, c in enumerate(ctxs):
+        kk = torch.cat([k[b, :c].double().cpu(), kn[b:b + 1]])
+        vv = torch.cat([v[b, :c].double().cpu(), vn[b:b + 1]])
+        att[b] = ref_attention(q[b:b + 1], kk, vv, c, 1, window)[0]
+    att = r16(att.reshape(M, No))
+    want = xd + att @ w_out.double().cpu().T + z(bo, D) + h @ w_down.double().cpu().T + z(bd, D)
+    got = x.double().cpu()
+    assert torch.isfinite(got).all()
+    err = (got - want).abs().max().item()
+    assert err <= 2 ** -6 * max(1.0, (want - xd).abs().max().item()), (err, (want - xd).abs().max().item())
+    # the cache: the new rows, and nothing else
+    for b, c in enumerate(ctxs):
+        page = int(table[b, c // PAGE])
+        assert (kc[page, :, c % PAGE].double().cpu() - kn[b]).abs().max() <= 2 ** -7 * max(1.0, kn[b].abs().max().item()), b
+        assert (vc[page, :, c % PAGE].double().cpu() - vn[b]).abs().max() <= 2 ** -7 * max(1.0, vn[b].abs().max().item()), b
+        kc0[page, :, c % PAGE] = kc[page, :, c % PAGE]
+        vc0[page, :, c % PAGE] = vc[page, :, c % PAGE]
+    same = lambda a_, b2: torch.equal(a_.view(torch.int16), b2.view(torch.int16))
+    assert same(kc, kc0) and same(vc, vc0), "the kernel wrote to the cache outside the new tokens' rows"
