@@ -22,9 +22,9 @@ struct SampleArgs {
     int* recent_n;            // [*] how many of them are valid
     unsigned long long* rng;  // [*] generator state, advanced by one draw when a draw is made
     int* out;                 // [B] chosen token
-    float* sort_key;          // [B, vpad] scratch for the whole-row nucleus, or null
-    int* sort_idx;            // [B, vpad]
-    int B, V, vpad;           // vpad: a power of two >= V
+    float* sort_key;          // unused (the whole-row nucleus once sorted its candidates here); kept for the layout
+    int* sort_idx;            // unused
+    int B, V, vpad;           // vpad: unused
     int top_k;                // <= 0: all tokens
     float temperature, top_p, min_p, repeat_penalty;
 };
@@ -104,6 +104,184 @@ __device__ float block_scan(float v, float* sw, float* total) {
     return v + before;
 }
 
+
+// ---------------------------------------------------------------------------
+// Helpers of the whole-row nucleus: mass in fixed point, prefixes of the order
+// "weight descending, index ascending" found without sorting.
+// ---------------------------------------------------------------------------
+#define SM_FIX 17592186044416.0          /* 2^44: weights are <= 1, a row has < 2^19 of them */
+// a weight (0 <= p <= 1) in units of 2^-44, from its bits: integer work only, one such conversion per
+// element and pass adds up (64-bit floating point is slow on this part)
+__device__ __forceinline__ unsigned long long to_fixed(float p) {
+    const unsigned u = __float_as_uint(p);
+    const int e = (int)((u >> 23) & 255u);
+    const unsigned long long m = (u & 0x7fffffu) | (e ? 0x800000u : 0u);
+    const int sh = (e ? e : 1) - 106;                     // 2^(e-127) * m * 2^-23 * 2^44
+    if (sh >= 0) return m << sh;
+    return sh > -64 ? m >> (-sh) : 0ull;
+}
+__device__ __forceinline__ unsigned long long to_fixed_sum(float p) {       // a sum of weights: may exceed 1
+    const double v = (double)p * SM_FIX;
+    return v <= 0.0 ? 0ull : (unsigned long long)v;
+}
+__device__ __forceinline__ float from_fixed(unsigned long long v) { return (float)((double)v / SM_FIX); }
+
+// f(i, w[i]) for every element of the row that falls to this thread, eight loads under way at a time: a
+// loop that loads, then adds to a histogram, then loads again waits out a trip to L2 per element
+template <typename F>
+__device__ __forceinline__ void for_row(const float* w, int V, F f) {
+    for (int base = threadIdx.x; base < V; base += SM_THREADS * 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = base + k * SM_THREADS;
+            v[k] = i < V ? w[i] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = base + k * SM_THREADS;
+            if (i < V) f(i, v[k]);
+        }
+    }
+}
+
+// sum of one 64-bit integer per thread; every thread gets the total
+__device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* sw) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) sw[w] = v;
+    __syncthreads();
+    unsigned long long t = 0;
+    for (int k = 0; k < SM_THREADS / 32; ++k) t += sw[k];
+    __syncthreads();
+    return t;
+}
+
+// A prefix of the order: every weight whose bits exceed `key`, and the first `among` (by index) of the
+// weights whose bits equal it; `mass` is the prefix's mass.  found false: no prefix's mass exceeds the goal.
+struct Boundary { unsigned key; unsigned among; unsigned long long mass; bool found; };
+struct SelectShared { unsigned prefix; unsigned long long above; int bin; int found; unsigned rank; int token; };
+
+// The shortest prefix (in the order above) of the candidates (weights >= low; with `within`, only the
+// elements of that prefix) whose mass exceeds `goal`.  hist: [32 warps][256] 64-bit words.
+__device__ Boundary select_prefix(const float* w, int V, float low, const Boundary* within, unsigned long long goal,
+                                  unsigned long long* hist, unsigned long long* s_u64, SelectShared* sh) {
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
+    Boundary out;
+    out.found = false; out.key = 0; out.among = 0; out.mass = 0;
+    if (tid == 0) { sh->prefix = 0; sh->above = 0; sh->found = 1; }
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = tid; i < 32 * 256; i += SM_THREADS) hist[i] = 0;
+        __syncthreads();
+        const unsigned prefix = sh->prefix;
+        const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+        unsigned long long* mine = hist + wp * 256;
+        const unsigned wkey = within ? within->key : 0u;
+        for_row(w, V, [&](int, float pv) {
+            const unsigned key = __float_as_uint(pv);
+            if (pv < low || (key & mask) != prefix) return;
+            if (within && key <= wkey) return;                   // what lies at the prefix's own boundary is added below
+            // (one histogram per warp.  Adding the lanes' mass together first, where they hit the same
+            // bin, was tried and is slower: 230 against 165 us a row, the shuffles cost more than the
+            // collisions they avoid.)
+            atomicAdd(mine + ((key >> shift) & 255u), to_fixed(pv));
+        });
+        __syncthreads();
+        // the boundary weight of `within`: its first `among` elements count, as one lump in their bin
+        if (within && tid == 0 && (within->key & mask) == prefix && __uint_as_float(within->key) >= low)
+            hist[(within->key >> shift) & 255u] += (unsigned long long)within->among * to_fixed(__uint_as_float(within->key));
+        __syncthreads();
+        unsigned long long t = 0;                                 // the 32 warps' histograms into the first
+        if (tid < 256)
+            for (int k = 0; k < 32; ++k) t += hist[k * 256 + tid];
+        __syncthreads();
+        if (tid < 256) hist[tid] = t;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long above = sh->above;
+            int bin = 255;
+            for (; bin >= 0; --bin) {
+                if (above + hist[bin] > goal) break;
+                above += hist[bin];
+            }
+            sh->bin = bin;
+            if (bin >= 0) { sh->above = above; sh->prefix = prefix | ((unsigned)bin << shift); }
+            else sh->found = 0;
+        }
+        __syncthreads();
+        if (!sh->found) return out;
+    }
+    // all 32 bits are known: how many of the equal weights it takes to pass the goal
+    const unsigned key = sh->prefix;
+    const unsigned long long each = to_fixed(__uint_as_float(key)), above = sh->above;
+    const unsigned long long n = each > 0 ? (goal - above) / each + 1 : 1;
+    out.found = true;
+    out.key = key;
+    out.among = (unsigned)n;
+    out.mass = above + n * each;
+    (void)lane; (void)wp; (void)s_u64;
+    return out;
+}
+
+// index of the e-th (1-based, by index ascending) weight whose bits equal `key`; each thread takes a run of
+// consecutive indices, so the equals before a thread's run are one scan away
+__device__ int kth_equal(const float* w, int V, unsigned key, unsigned e, float* s_f, SelectShared* sh) {
+    const int tid = threadIdx.x;
+    const int per = (V + SM_THREADS - 1) / SM_THREADS;
+    const int i0 = min(V, tid * per), i1 = min(V, i0 + per);
+    int mine = 0;
+    for (int b0 = i0; b0 < i1; b0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = b0 + k < i1 ? w[b0 + k] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mine += (b0 + k < i1 && __float_as_uint(v[k]) == key) ? 1 : 0;
+    }
+    if (tid == 0) sh->token = -1;
+    float total;
+    const int upto = (int)block_scan((float)mine, s_f, &total);        // counts are far below 2^24: exact in float
+    __syncthreads();
+    const int before = upto - mine;
+    if ((unsigned)before < e && e <= (unsigned)upto) {
+        int seen = before;
+        for (int i = i0; i < i1; ++i)
+            if (__float_as_uint(w[i]) == key && (unsigned)(++seen) == e) { sh->token = i; break; }
+    }
+    __syncthreads();
+    int token = sh->token;
+    __syncthreads();
+    if (token < 0) {
+        // fewer than e equals (cannot happen for a boundary that select_prefix returned): the last of them
+        int last = -1;
+        for (int i = i0; i < i1; ++i) if (__float_as_uint(w[i]) == key) last = i;
+        atomicMax(&sh->token, last);
+        __syncthreads();
+        token = max(sh->token, 0);
+    }
+    return token;
+}
+
+// the candidate that sorts last: the smallest weight >= low, the highest index among equals
+__device__ int last_candidate(const float* w, int V, float low, float* s_f, int* s_i, SelectShared* sh) {
+    const int tid = threadIdx.x;
+    float mn = INFINITY;
+    for (int i = tid; i < V; i += SM_THREADS) { const float pv = w[i]; if (pv >= low) mn = fminf(mn, pv); }
+    float bv; int bi;
+    block_argmax(-mn, tid, s_f, s_i, &bv, &bi);                  // (thread 0 publishes through the two words below)
+    __syncthreads();
+    if (tid == 0) { sh->rank = __float_as_uint(-bv); sh->token = -1; }
+    __syncthreads();
+    const unsigned key = sh->rank;
+    int last = -1;
+    for (int i = tid; i < V; i += SM_THREADS) if (__float_as_uint(w[i]) == key) last = max(last, i);
+    atomicMax(&sh->token, last);
+    __syncthreads();
+    return max(sh->token, 0);
+}
+
 __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(SampleArgs a) {
     __shared__ float s_f[32];
@@ -115,6 +293,10 @@ sample_kernel(SampleArgs a) {
     __shared__ float c_val[SM_KMAX];
     __shared__ int c_idx[SM_KMAX];
     __shared__ int s_found;
+    __shared__ unsigned long long s_u64[32];
+    __shared__ SelectShared s_sel_obj;
+    SelectShared* s_sel = &s_sel_obj;
+    extern __shared__ unsigned long long hist[];          // [32][256], the whole-row nucleus only
 
     const int b = blockIdx.x, tid = threadIdx.x, V = a.V;
     gl_grid_launch_dependents();
@@ -343,93 +525,43 @@ sample_kernel(SampleArgs a) {
         return;
     }
     if (a.top_p < 1.0f || a.min_p > 0.f) {
-        // 5. nucleus over the whole row (sampleTopPFromWeights, sampling.go:171-228): candidates are
-        //    the weights >= 1e-5 of the largest (all of them if that set holds less than top_p of the
-        //    mass), sorted by weight descending then index ascending; min-p and top-p cut the sorted
-        //    list; one draw over what is kept.
-        float* ck = a.sort_key + (size_t)b * a.vpad;
-        int* ci = a.sort_idx + (size_t)b * a.vpad;
+        // 5. nucleus over the whole row (sampleTopPFromWeights, sampling.go:171-228).  The reference sorts
+        //    the candidates (the weights >= 1e-5 of the largest; all of them if that set holds less than
+        //    top_p of the mass) by weight descending then index ascending, cuts the list at the first
+        //    weight below min_p times the best and at the shortest prefix whose mass exceeds top_p times
+        //    the total, and draws from what is kept.  A prefix of that order is "every weight above some
+        //    value, and the first few, by index, of the weights equal to it", so nothing is sorted here:
+        //    the value is found digit by digit (four passes of 256-bin histograms of mass over the bits
+        //    of the weights), once for the cut and once for the draw.  Mass is added up in 64-bit fixed
+        //    point, so the sums do not depend on the order of the additions.
         float mxp = 0.f;
-        for (int i = tid; i < V; i += SM_THREADS) mxp = fmaxf(mxp, w[i]);
-        int dummy;
-        block_argmax(mxp, tid, s_f, s_i, &s_best, &dummy);
-        const float thr = s_best * 1e-5f;
-        if (tid == 0) { s_ngt = 0; }
-        __syncthreads();
-        float kpart = 0.f;
-        for (int i = tid; i < V; i += SM_THREADS) {
-            const float p = w[i];
-            if (p >= thr) {
-                const unsigned slot = atomicAdd(&s_ngt, 1u);
-                ck[slot] = p; ci[slot] = i;
-                kpart += p;
-            }
-        }
-        float kept_sum;
-        block_scan(kpart, s_f, &kept_sum);
-        __syncthreads();
-        int n_c = (int)s_ngt;
-        if (kept_sum < a.top_p * sum) {                  // too little mass: every token is a candidate
-            for (int i = tid; i < V; i += SM_THREADS) { ck[i] = w[i]; ci[i] = i; }
-            n_c = V;
-        }
-        int np = 1;
-        while (np < n_c) np <<= 1;
-        for (int i = n_c + tid; i < np; i += SM_THREADS) { ck[i] = -1.f; ci[i] = 0x7fffffff; }
-        // bitonic sort in global memory (the row's candidates stay in L2), best first
-        for (int size = 2; size <= np; size <<= 1) {
-            for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                __syncthreads();
-                for (int t = tid; t < np / 2; t += SM_THREADS) {
-                    const int lo_i = 2 * t - (t & (stride - 1)), hi_i = lo_i + stride;
-                    const bool up = (lo_i & size) == 0;
-                    const float v0 = ck[lo_i], v1 = ck[hi_i];
-                    const int i0 = ci[lo_i], i1 = ci[hi_i];
-                    const bool first_better = v0 > v1 || (v0 == v1 && i0 < i1);
-                    if (first_better != up) { ck[lo_i] = v1; ck[hi_i] = v0; ci[lo_i] = i1; ci[hi_i] = i0; }
-                }
-            }
-        }
-        __syncthreads();
+        for_row(w, V, [&](int, float pv) { mxp = fmaxf(mxp, pv); });
+        block_argmax(mxp, tid, s_f, s_i, &s_best, &s_besti);
+        const float best = s_best;
+        const float thr = best * 1e-5f;
+        // the candidates: weights >= thr if they carry top_p of the mass, else all
+        unsigned long long part_fx = 0;
+        for_row(w, V, [&](int, float pv) { if (pv >= thr) part_fx += to_fixed(pv); });
+        const float kept_sum = from_fixed(block_sum_u64(part_fx, s_u64));
+        float low = (kept_sum < a.top_p * sum) ? 0.f : thr;          // weights below `low` are not candidates
         // min-p: the list ends before the first weight below min_p * best; its mass is the new total
-        int cutoff = n_c;
         float total = sum;
         if (a.min_p > 0.f) {
-            const float mthr = a.min_p * ck[0];
-            if (tid == 0) s_found = n_c;
-            __syncthreads();
-            for (int i = tid; i < n_c; i += SM_THREADS)
-                if (i > 0 && ck[i] < mthr) atomicMin(&s_found, i);
-            __syncthreads();
-            cutoff = s_found;
-            float mpart = 0.f;
-            for (int i = tid; i < cutoff; i += SM_THREADS) mpart += ck[i];
-            block_scan(mpart, s_f, &total);
-            __syncthreads();
+            low = fmaxf(low, a.min_p * best);
+            unsigned long long m_fx = 0;
+            for_row(w, V, [&](int, float pv) { if (pv >= low) m_fx += to_fixed(pv); });
+            total = from_fixed(block_sum_u64(m_fx, s_u64));
         }
         // top-p: the shortest prefix whose mass exceeds top_p * total
         const float target = a.top_p * total;
-        if (tid == 0) { s_found = 0x7fffffff; s_besti = 0; }
-        __syncthreads();
-        float carry = 0.f, kept = 0.f;
-        for (int base = 0; base < cutoff; base += SM_THREADS) {
-            const int i = base + tid;
-            const float p = i < cutoff ? ck[i] : 0.f;
-            float tot;
-            const float incl = block_scan(p, s_f, &tot) + carry;
-            if (i < cutoff && incl > target) { atomicMin(&s_found, i); s_besti = 1; }
-            carry += tot;
-            __syncthreads();
-            if (s_besti) break;
-        }
-        __syncthreads();
-        if (s_found != 0x7fffffff) cutoff = s_found + 1;
-        // the kept mass: the running sum up to the cut
-        {
-            float kp = 0.f;
-            for (int i = tid; i < cutoff; i += SM_THREADS) kp += ck[i];
-            block_scan(kp, s_f, &kept);
-            __syncthreads();
+        Boundary cut = select_prefix(w, V, low, nullptr, to_fixed_sum(target), hist, s_u64, s_sel);
+        float kept;
+        if (cut.found) {
+            kept = from_fixed(cut.mass);
+        } else {                                                      // never exceeded: everything is kept
+            unsigned long long m_fx = 0;
+            for_row(w, V, [&](int, float pv) { if (pv >= low) m_fx += to_fixed(pv); });
+            kept = from_fixed(block_sum_u64(m_fx, s_u64));
         }
         if (!(kept > 0.f) || !finite_bits(kept)) {
             if (tid == 0) finish(a, b, row, imax);
@@ -439,24 +571,16 @@ sample_kernel(SampleArgs a) {
             unsigned long long st = a.rng[row];
             s_best = rng_next(&st) * kept;
             a.rng[row] = st;
-            s_found = cutoff - 1;
-            s_besti = 0;
         }
         __syncthreads();
         const float rr = s_best;
-        carry = 0.f;
-        for (int base = 0; base < cutoff; base += SM_THREADS) {
-            const int i = base + tid;
-            const float p = i < cutoff ? ck[i] : 0.f;
-            float tot;
-            const float incl = block_scan(p, s_f, &tot) + carry;
-            if (i < cutoff && incl > rr) { atomicMin(&s_found, i); s_besti = 1; }
-            carry += tot;
-            __syncthreads();
-            if (s_besti) break;
-        }
-        __syncthreads();
-        if (tid == 0) finish(a, b, row, ci[s_found]);
+        // the draw: the first element of the kept prefix, in the same order, whose running mass exceeds rr
+        Boundary pick = select_prefix(w, V, low, cut.found ? &cut : nullptr, to_fixed_sum(rr), hist, s_u64, s_sel);
+        int token;
+        if (pick.found) token = kth_equal(w, V, pick.key, pick.among, s_f, s_sel);
+        else if (cut.found) token = kth_equal(w, V, cut.key, cut.among, s_f, s_sel);     // the list's last element
+        else token = last_candidate(w, V, low, s_f, s_i, s_sel);
+        if (tid == 0) finish(a, b, row, token);
         return;
     }
     float r = 0.f;
@@ -490,11 +614,22 @@ GL_API int gl_sample(const SampleArgs* args, cudaStream_t stream) {
     if (a.B <= 0) return GL_OK;
     if (a.V <= 0) return GL_ERR_SHAPE;
     const bool greedy = a.temperature < 1e-6f || a.top_k == 1;
+    size_t smem = 0;
     if (!greedy) {
         if (a.top_k > SM_KMAX && a.top_k < a.V) return GL_ERR_SHAPE;
         const bool whole_row = !(a.top_k > 0 && a.top_k < a.V);
-        if (whole_row && (a.top_p < 1.0f || a.min_p > 0.f) && (!a.sort_key || !a.sort_idx || a.vpad < a.V))
-            return GL_ERR_SHAPE;
+        if (whole_row && (a.top_p < 1.0f || a.min_p > 0.f)) {
+            // the nucleus over the whole row keeps a histogram of mass per warp
+            smem = 32 * 256 * sizeof(unsigned long long);
+            static bool configured = false;
+            if (!configured) {
+                if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+                    cudaGetLastError();
+                    return GL_ERR_SMEM;
+                }
+                configured = true;
+            }
+        }
     }
-    return gl_launch(sample_kernel, dim3(a.B), dim3(SM_THREADS), 0, stream, 1, a);
+    return gl_launch(sample_kernel, dim3(a.B), dim3(SM_THREADS), smem, stream, 1, a);
 }

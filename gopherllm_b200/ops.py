@@ -789,9 +789,9 @@ def check_sampler(temperature: float, top_k: int, top_p: float, min_p: float, vo
 
 
 def needs_sort_scratch(temperature: float, top_k: int, top_p: float, min_p: float, vocab: int) -> bool:
-    """True when sampling sorts whole rows (a nucleus or min-p cut with top-k off)."""
-    greedy = temperature < 1e-6 or top_k == 1
-    return (not greedy) and not (0 < top_k < vocab) and (top_p < 1.0 or min_p > 0.0)
+    """Whether sampling needs sorting scratch: never (a nucleus or min-p cut with top-k off finds its
+    boundary by a search over the weights' bits, not by sorting the row)."""
+    return False
 
 
 def sort_scratch_size(vocab: int) -> int:

@@ -539,6 +539,9 @@ def test_sampling_matches_plain(V):
     logits[1, 7] = np.nan
     logits[2, 3] = np.inf
     logits[3, : V // 2] = logits[3, V // 2 - 1]          # many equal values
+    if V >= 1000:                                        # one token far above a flat rest: the rest's weights fall
+        logits[4] = (rng.standard_normal(V) * 0.01).astype(np.float32)     # under 1e-5 of the best, yet carry mass
+        logits[4, 17] = 12.0
     recents = [list(rng.integers(0, V, size=n)) for n in (0, 5, 64, 64, 30)]
     recents[2][5] = recents[2][9]                        # a token twice in the window
     cases = [dict(temperature=0.0, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0),
@@ -553,7 +556,10 @@ def test_sampling_matches_plain(V):
              dict(temperature=0.7, top_k=0, top_p=0.9, min_p=0.0, repeat_penalty=1.1),
              dict(temperature=1.3, top_k=0, top_p=0.5, min_p=0.1, repeat_penalty=1.0),
              dict(temperature=0.4, top_k=0, top_p=1.0, min_p=0.3, repeat_penalty=1.0),
-             dict(temperature=5.0, top_k=V, top_p=0.97, min_p=0.0, repeat_penalty=1.0)]
+             dict(temperature=5.0, top_k=V, top_p=0.97, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=1.0, top_k=0, top_p=0.999, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=2.5, top_k=0, top_p=0.3, min_p=0.0, repeat_penalty=1.0),
+             dict(temperature=1.0, top_k=0, top_p=1.0, min_p=0.02, repeat_penalty=1.15)]
     for ci, c in enumerate(cases):
         if c["top_k"] > 0 and c["top_k"] >= V and (c["top_p"] < 1 or c["min_p"] > 0):
             continue
@@ -567,7 +573,7 @@ def test_sampling_matches_plain(V):
         seeds = [11 + ci, 0xDEADBEEFCAFE1337, 3, 2 ** 63 + 5, 99]
         rng_state = torch.tensor([s - 2 ** 64 if s >= 2 ** 63 else s for s in seeds], dtype=torch.int64, device=DEV)
         out = torch.zeros(B, dtype=torch.int32, device=DEV)
-        draws = 3
+        draws = 6 if c["top_k"] == 0 else 3
         got = []
         for _ in range(draws):
             o.sample(dl, work, recent, recent_n, rng_state, out, **c)
@@ -600,6 +606,48 @@ def test_sampling_matches_plain(V):
                     slack = V * 2.0 ** -24
                     lo_edge = cdf[g_ - 1] if g_ > 0 else 0.0
                     assert lo_edge - slack <= u <= cdf[g_] + slack, (ci, i, d, g_, want, u, lo_edge, cdf[g_])
+                    want = g_
+                if nucleus and got[d][i] != want:
+                    # The reference walks running 32-bit sums over the sorted candidates, one by one; the
+                    # kernel adds mass exactly (fixed point).  Over thousands of candidates the two differ
+                    # by up to n * 2^-24 of the total, more than a tail candidate's weight, so the cut and
+                    # the draw may fall a few candidates apart.  The kernel's token must then be right for
+                    # the exact sums: inside the exact cut (give or take that slack), with the draw u * kept
+                    # inside its interval of the exact running mass, give or take the same.
+                    u = float(plain_phi.Rng(state_before).next_f32())
+                    lg = logits[i].astype(np.float32).copy()
+                    lg[~np.isfinite(lg)] = -np.inf
+                    pen = np.float32(c["repeat_penalty"])
+                    for tok in rec:
+                        if lg[tok] > -np.inf and pen != 1:
+                            lg[tok] = lg[tok] / pen if lg[tok] > 0 else lg[tok] * pen
+                    inv_t = np.float32(1.0) / np.float32(c["temperature"])
+                    wts = np.exp(((lg - lg.max()) * inv_t).astype(np.float64)).astype(np.float32).astype(np.float64)
+                    total = wts.sum()
+                    thr = np.float64(np.float32(wts.max()) * np.float32(1e-5))
+                    cand = np.nonzero(wts >= thr)[0]
+                    if wts[cand].sum() < np.float64(np.float32(c["top_p"])) * total:
+                        cand = np.arange(V)
+                    order = cand[np.lexsort((cand, -wts[cand]))]
+                    sw = wts[order]
+                    n_c = len(order)
+                    if c["min_p"] > 0:
+                        keep = sw >= np.float64(np.float32(c["min_p"]) * np.float32(sw[0]))
+                        n_c = int(keep.sum())
+                        total = sw[:n_c].sum()
+                    cs = np.cumsum(sw[:n_c])
+                    slack = n_c * 2.0 ** -24 * total
+                    target = np.float64(np.float32(c["top_p"])) * total
+                    over = np.nonzero(cs > target + slack)[0]
+                    cut_hi = int(over[0]) + 1 if len(over) else n_c            # the cut is at most here ...
+                    over = np.nonzero(cs > target - slack)[0]
+                    cut_lo = int(over[0]) + 1 if len(over) else n_c            # ... and at least here
+                    g_ = got[d][i]
+                    pos = int(np.nonzero(order[:n_c] == g_)[0][0]) if g_ in order[:n_c] else -1
+                    assert 0 <= pos < cut_hi, (ci, i, d, g_, want, pos, cut_lo, cut_hi)
+                    lo_edge = cs[pos - 1] if pos > 0 else 0.0
+                    ok = any(lo_edge - slack <= u * cs[cut - 1] <= cs[pos] + slack for cut in {cut_lo, cut_hi})
+                    assert ok or pos == cut_hi - 1, (ci, i, d, g_, want, pos, u, lo_edge, cs[pos], cs[cut_lo - 1], cs[cut_hi - 1])
                     want = g_
                 assert got[d][i] == want, (ci, i, d, got[d][i], want)
                 rec = (rec + [want])[-64:]
