@@ -22,6 +22,7 @@ struct AttnArgs {
     const int* pages;         // [B, max_pages]
     int B, nH, nKV, hd, max_pages, window, max_qlen;
     float score_scale;
+    int n_pages;              // pages of the cache entry (read by builds that check indices; 0: unknown)
 };
 
 #define AG_ROWS 8
@@ -62,7 +63,7 @@ attn_generic_kernel(AttnArgs a) {
 
     const int* pg = a.pages + (size_t)b * a.max_pages;
     for (int page_i = lo_cta / GL_PAGE; page_i <= p_last / GL_PAGE; ++page_i) {
-        const int page = pg[page_i];
+        const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + g) * GL_PAGE * hd;
         const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + g) * GL_PAGE * hd;
         const int j0 = page_i * GL_PAGE;

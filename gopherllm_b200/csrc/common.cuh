@@ -78,6 +78,34 @@ static int gl_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
 }
 #endif
 
+// A build with -DGL_DEBUG_BOUNDS checks the indices that kernels take from memory (token ids, page
+// numbers, positions within a page table) before they use them.  A bad index is recorded (which kind,
+// its value, the limit it broke, how many were seen) in a word the host reads, and the access is made at
+// index 0 instead: the kernel runs on with a wrong result and an error on record, it never traps and
+// never touches memory outside its buffers.  The host checks the same things before a step is launched;
+// this is the second net, for an index that a kernel or a caller of the C entry points got wrong.
+enum GlBoundsKind { GL_BAD_TOKEN = 1, GL_BAD_PAGE = 2, GL_BAD_POSITION = 3, GL_BAD_ROW = 4 };
+#if defined(GL_DEBUG_BOUNDS) && defined(__CUDACC__)
+__device__ int gl_bounds_word[4];      // [0] kind of the first bad index (0: none), [1] its value, [2] the limit, [3] how many
+__device__ __forceinline__ int gl_checked(int v, int limit, int kind) {
+    if ((unsigned)v < (unsigned)limit) return v;
+    if (atomicCAS(&gl_bounds_word[0], 0, kind) == 0) { gl_bounds_word[1] = v; gl_bounds_word[2] = limit; }
+    atomicAdd(&gl_bounds_word[3], 1);
+    return 0;
+}
+// out4 receives the four words; clear sets them back to zero.  -1 if they could not be read.
+GL_API int gl_bounds_status(int* out4, int clear) {
+    if (cudaMemcpyFromSymbol(out4, gl_bounds_word, 4 * sizeof(int)) != cudaSuccess) return -1;
+    if (clear && out4[0] != 0) {
+        const int zero[4] = {0, 0, 0, 0};
+        if (cudaMemcpyToSymbol(gl_bounds_word, zero, sizeof(zero)) != cudaSuccess) return -1;
+    }
+    return 0;
+}
+#else
+#define gl_checked(v, limit, kind) (v)
+#endif
+
 static inline int gl_check_launch() {
     return cudaGetLastError() == cudaSuccess ? GL_OK : GL_ERR_LAUNCH;
 }

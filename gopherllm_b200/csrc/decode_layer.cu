@@ -323,7 +323,8 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
                 const int cnt = min(nb - pi, a1 - L);
                 for (int j0 = 0; j0 < cnt; j0 += 32) {
                     const int mine = j0 + lane;
-                    const int pg = mine < cnt ? p.pages[(size_t)b * p.max_pages + s_first[b] + pi + mine] : 0;
+                    const int pg = mine < cnt ? gl_checked(p.pages[(size_t)b * p.max_pages + gl_checked(s_first[b] + pi + mine, p.max_pages, GL_BAD_POSITION)],
+                                                           p.n_pages, GL_BAD_PAGE) : 0;
                     const int n = min(32, cnt - j0);
                     for (int j = 0; j < n; ++j) {
                         const int id = __shfl_sync(0xffffffffu, pg, j);
@@ -613,7 +614,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
                         const uint4 val = ad_rotated_chunk(head, cc, is_v ? 0 : p.half, is_v ? nullptr : cs,
                                                            is_v ? nullptr : sn, 1.0f);
                         *(uint4*)((is_v ? sV : sK) + r * DL_ROWB + cc * 16) = val;
-                        const int id = p.pages[(size_t)b * p.max_pages + pabs];
+                        const int id = gl_checked(p.pages[(size_t)b * p.max_pages + gl_checked(pabs, p.max_pages, GL_BAD_POSITION)], p.n_pages, GL_BAD_PAGE);
                         __nv_bfloat16* cache = (__nv_bfloat16*)(is_v ? p.v_cache : p.k_cache);
                         *(uint4*)(cache + (size_t)id * page_stride + head_off + (size_t)r * DL_HD + cc * 8) = val;
                     }

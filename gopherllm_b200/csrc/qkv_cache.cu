@@ -47,6 +47,7 @@ struct QkvCacheArgs {
     int T, nH, nKV, hd, half, max_pages;
     int interleaved, norm_rms, write_kv;
     float eps, q_scale;
+    int n_pages;              // pages of the cache entry (read by builds that check indices; 0: unknown)
 };
 
 template <typename TA, typename TC>
@@ -106,7 +107,8 @@ __global__ void qkv_cache_kernel(QkvCacheArgs a) {
     } else {
         const int head = kind == 1 ? j - a.nH : j - a.nH - a.nKV;
         const int pos = a.tok_pos[t];
-        const int page = a.pages[(size_t)a.tok_seq[t] * a.max_pages + pos / GL_PAGE];
+        const int slot = gl_checked(pos / GL_PAGE, a.max_pages, GL_BAD_POSITION);
+        const int page = gl_checked(a.pages[(size_t)a.tok_seq[t] * a.max_pages + slot], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         TC* base = (TC*)(kind == 1 ? a.k_cache : a.v_cache);
         TC* dst = base + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * hd;
         for (int d = lane; d < hd; d += 32) gl_store(dst + d, v[d]);
@@ -131,8 +133,10 @@ qkv_cache_bf16_kernel(QkvCacheArgs a) {
     const float* cs_row = a.cosv ? a.cosv + (size_t)t * a.half : nullptr;
     const float* sn_row = a.sinv ? a.sinv + (size_t)t * a.half : nullptr;
     const int pos = a.tok_pos[t];
+    const int slot = gl_checked(pos / GL_PAGE, a.max_pages, GL_BAD_POSITION);
     const size_t cache_row = a.write_kv
-        ? ((size_t)a.pages[(size_t)a.tok_seq[t] * a.max_pages + pos / GL_PAGE] * a.nKV * GL_PAGE + (pos % GL_PAGE)) * a.hd : 0;
+        ? ((size_t)gl_checked(a.pages[(size_t)a.tok_seq[t] * a.max_pages + slot], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE)
+           * a.nKV * GL_PAGE + (pos % GL_PAGE)) * a.hd : 0;
     for (unsigned i = threadIdx.x; i < n; i += blockDim.x) {
         const unsigned j = i / chunks, c = i - j * chunks;
         const int kind = j < (unsigned)a.nH ? 0 : (j < (unsigned)(a.nH + a.nKV) ? 1 : 2);

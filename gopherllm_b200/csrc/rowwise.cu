@@ -13,7 +13,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
     const int t = blockIdx.x;
     gl_grid_launch_dependents();
     gl_grid_wait();
-    int tok = tokens[t];
+    int tok = gl_checked(tokens[t], V, GL_BAD_TOKEN);
     // ids are checked on the host; a bad id must still not read outside the table
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
     const TW* row = table + (size_t)tok * D;
@@ -44,7 +44,7 @@ __global__ void add_rows_kernel(const TW* __restrict__ table, const int* __restr
     const int t = blockIdx.x;
     gl_grid_launch_dependents();
     gl_grid_wait();
-    int i = index[t];
+    int i = gl_checked(index[t], N, GL_BAD_ROW);
     i = i < 0 ? 0 : (i >= N ? N - 1 : i);        // checked on the host; never read outside the table
     const TW* row = table + (size_t)i * D;
     float* o = out + (size_t)t * D;

@@ -8,6 +8,7 @@ not build, is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, byref, c_float, c_int, c_void_p
 from typing import Optional
 
@@ -86,9 +87,14 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
 
 
 _LIBS: dict = {}
+# GOPHERLLM_DEBUG_BOUNDS=1 selects builds of the kernels that check the indices they take from memory
+# (token ids, page numbers, positions) and record a bad one instead of using it; see bounds_status().
+DEBUG_BOUNDS = os.environ.get("GOPHERLLM_DEBUG_BOUNDS", "") not in ("", "0")
 
 
 def _lib(source: str, defines=()):
+    if DEBUG_BOUNDS:
+        defines = tuple(defines) + ("GL_DEBUG_BOUNDS=1",)
     key = (source, tuple(defines))
     lib = _LIBS.get(key)
     if lib is None:
@@ -192,7 +198,7 @@ class _QkvCacheArgs(Structure):
                 ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("pages", c_void_p),
                 ("T", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("half", c_int),
                 ("max_pages", c_int), ("interleaved", c_int), ("norm_rms", c_int), ("write_kv", c_int),
-                ("eps", c_float), ("q_scale", c_float)]
+                ("eps", c_float), ("q_scale", c_float), ("n_pages", c_int)]
 
 
 def qkv_to_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -240,7 +246,7 @@ def qkv_to_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, 
                       tok_seq.data_ptr(), tok_pos.data_ptr(), pages.data_ptr(),
                       T, num_heads, num_kv_heads, head_dim, half, pages.shape[-1],
                       1 if interleaved else 0, 1 if norm_rms else 0, 1 if write_kv else 0,
-                      norm_eps, q_scale)
+                      norm_eps, q_scale, k_cache.shape[0])
     fn = _lib("qkv_cache.cu").gl_qkv_cache
     _check(fn(byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "qkv_to_cache")
@@ -250,7 +256,9 @@ class _AttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("max_pages", c_int),
-                ("window", c_int), ("max_qlen", c_int), ("score_scale", c_float)]
+                ("window", c_int), ("max_qlen", c_int), ("score_scale", c_float),
+                # (appended: the kernels that check indices read it, the others' records end before it)
+                ("n_pages", c_int)]
 
 
 def _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
@@ -272,7 +280,8 @@ def _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
         raise KernelError(f"{num_heads} heads are not a multiple of {num_kv_heads} key/value heads")
     return _AttnArgs(q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                      seq_qstart.data_ptr(), seq_qlen.data_ptr(), seq_ctx.data_ptr(), pages.data_ptr(),
-                     B, num_heads, num_kv_heads, head_dim, pages.shape[-1], window, max_qlen, score_scale)
+                     B, num_heads, num_kv_heads, head_dim, pages.shape[-1], window, max_qlen, score_scale,
+                     k_cache.shape[0])
 
 
 def attention_generic(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
@@ -714,9 +723,31 @@ def wait_failures(clear: bool = False) -> dict:
     return out
 
 
+_BOUNDS_KINDS = {1: "token id", 2: "page number", 3: "position in a page table", 4: "row of a table"}
+
+
+def bounds_status(clear: bool = False) -> dict:
+    """In a build that checks indices (GOPHERLLM_DEBUG_BOUNDS=1): library name -> (kind, value, limit,
+    count) of the bad indices its kernels met since the words were last cleared; libraries without
+    violations are left out.  Empty in an ordinary build."""
+    out = {}
+    for key, lib in list(build._loaded.items()):
+        if hasattr(lib, "gl_bounds_status"):
+            words = (c_int * 4)()
+            if lib.gl_bounds_status(words, c_int(1 if clear else 0)) != 0:
+                out[key] = ("unreadable", 0, 0, 0)
+            elif words[0] != 0:
+                out[key] = (_BOUNDS_KINDS.get(words[0], str(words[0])), words[1], words[2], words[3])
+    return out
+
+
 def check_wait_failures() -> None:
     """Raise KernelError naming every library whose kernels gave up a bounded wait since the last
     check; the words are cleared, so the next check speaks of what ran after this one."""
+    oob = bounds_status(clear=True)
+    if oob:
+        raise KernelError("kernels met indices outside their tables: " + "; ".join(
+            f"{lib}: {kind} {value} (limit {limit}, {count} in all)" for lib, (kind, value, limit, count) in sorted(oob.items())))
     bad = sorted(k for k, v in wait_failures(clear=True).items() if v != 0)
     if bad:
         reset_decode_layer_sync()
