@@ -484,6 +484,10 @@ DECODE_LAYER_MAX_ROWS = 64
 # Fewer tokens than this go through the separate kernels, which are faster there (measured on Phi-2's
 # sizes: 10 to 20 % at 1 to 16 tokens, equal at 32, the fused layer 3 to 6 % ahead at 48 and 64).
 DECODE_LAYER_MIN_ROWS = 33
+# ... and steps whose longest sequence is no longer than this: with few pages a sequence the fused
+# layer's per-head start and finish outweigh what it saves (64 sequences of 128 positions: 3.77 against
+# 3.58 ms a step; of 300: 4.30 against 4.40; of 2,048: 9.4 against 9.9).
+DECODE_LAYER_MIN_CONTEXT = 257
 DECODE_LAYER_MAX_HEAD_DIM = catalog.MAX_HEAD_DIM["decode_layer.cu"]
 USE_DECODE_LAYER = True
 _DECODE_LAYER_KEEP = None          # a dict here receives the work buffers of the last call (for tests)
@@ -491,13 +495,14 @@ _DECODE_LAYER_SYNC: dict = {}      # device index -> the int32 words the fused l
 
 
 def decode_layer_takes(x, w_qkv, w_up, w_out, w_down, cache_dtype, head_dim: int, group: int, rotary_half: int,
-                       interleaved: bool, head_norm: bool) -> bool:
+                       interleaved: bool, head_norm: bool, longest: int = 1 << 30) -> bool:
     """Whether the fused decode layer takes these types and sizes (the caller falls back to the separate
-    kernels otherwise): bfloat16 weights and cache, DECODE_LAYER_MIN_ROWS to 64 tokens, head sizes up to 128 in steps of 16,
+    kernels otherwise): bfloat16 weights and cache, DECODE_LAYER_MIN_ROWS to 64 tokens, a longest sequence
+    (``longest``, positions after the step) of at least DECODE_LAYER_MIN_CONTEXT, head sizes up to 128 in steps of 16,
     up to 8 query heads per key/value head, split-half rotation over a multiple of 16 dims, no per-head
     norm, widths that are multiples of 8."""
     return (USE_DECODE_LAYER and DECODE_LAYER_MIN_ROWS <= x.shape[0] <= DECODE_LAYER_MAX_ROWS
-            and cache_dtype == torch.bfloat16
+            and longest >= DECODE_LAYER_MIN_CONTEXT and cache_dtype == torch.bfloat16
             and all(w.dtype == torch.bfloat16 for w in (w_qkv, w_up, w_out, w_down))
             and head_dim % 16 == 0 and head_dim <= DECODE_LAYER_MAX_HEAD_DIM and group <= DECODE_MAX_GROUP
             and rotary_half % 8 == 0 and not interleaved and not head_norm

@@ -70,7 +70,8 @@ class ParallelBlock(AssembledBlock):
         w_up, b_up, act, w_down, b_down = self.ffn.fusable()
         half = 0 if m["cos"] is None else m["cos"].shape[1]
         if not ops.decode_layer_takes(x, m["w_qkv"], w_up, m["w_out"], w_down, m["k"].dtype, m["head_dim"],
-                                      m["num_heads"] // m["num_kv_heads"], half, m["interleaved"], m["head_norm"]):
+                                      m["num_heads"] // m["num_kv_heads"], half, m["interleaved"], m["head_norm"],
+                                      longest=ctx.max_len):
             return False
         g, b, eps, rms = self.norm.fusable()
         ops.decode_layer(x, g, b, eps, rms, m["w_qkv"], m["b_qkv"], w_up, b_up, act, m["w_out"], m["b_out"],

@@ -244,10 +244,10 @@ def test_captured_steps_are_kept_up_to_a_limit():
 def fused_layer_for_any_batch():
     """The fused decode layer is taken for more than 32 tokens by default; these tests want it from one."""
     from gopherllm_b200 import ops
-    old = ops.DECODE_LAYER_MIN_ROWS
-    ops.DECODE_LAYER_MIN_ROWS = 1
+    old = ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT
+    ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT = 1, 1
     yield ops
-    ops.DECODE_LAYER_MIN_ROWS = old
+    ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT = old
 
 
 def test_fused_decode_layer_whole_then_one_by_one(fused_layer_for_any_batch):
@@ -318,8 +318,9 @@ def test_forty_sequences_take_the_fused_decode_layer_by_default():
     cfg = tiny.TINY["D"][0]
     V = cfg["vocab_size"]
     rng = np.random.default_rng(19)
-    m = gl.load(tiny.folder("D"), dtype="bfloat16", max_tokens=40 * 128)
+    m = gl.load(tiny.folder("D"), dtype="bfloat16", max_tokens=40 * 128 + 320)
     lens = [int(n) for n in rng.integers(1, 100, size=40)]
+    lens[7] = 300                                          # one long sequence: the step's longest decides
     seqs = [tiny.prompt(rng, n + 3, V) for n in lens]
     slots = [m.open_sequence() for _ in seqs]
     launched = []
