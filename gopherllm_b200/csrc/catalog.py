@@ -4,8 +4,8 @@ from __future__ import annotations
 from typing import Iterable, Iterator, Tuple
 
 # libraries that do not depend on a model's sizes
-GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_tcgen05.cu",
-           "sampling.cu")
+GENERAL = ("rowwise.cu", "qkv_cache.cu", "attention_generic.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_stream.cu",
+           "gemm_tcgen05.cu", "sampling.cu")
 
 # libraries compiled once per head size (GL_HEAD_DIM)
 PER_HEAD_DIM: Tuple[str, ...] = ("attention_decode.cu", "attention_prefill.cu", "attention_prefill_tc.cu",

@@ -680,6 +680,45 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+STREAM_MIN_ROWS, STREAM_MAX_ROWS = 17, 64
+# Off: as measured with Phi-2's sizes the mma.sync product is as fast or faster at 17 to 64 rows (64 rows:
+# 19.5 / 29.8 / 39.9 µs for the qkv, the up and the joined out+down product against 19.8 / 25.7 / 25.7),
+# both far from the weights' streaming time; what a block pays once (tensor-memory allocation, two cluster
+# barriers, the reduction through the peers' shared memory) stands against ten to twenty stages of work.
+USE_GEMM_STREAM = False
+
+
+def gemm_stream(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
+                add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
+                out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
+                split_k: int = 0, second=None) -> torch.Tensor:
+    """The weight-streaming product for up to 64 rows on the 5th-generation tensor cores: the weights
+    are the 128-row operand of tcgen05.mma, the tokens its N (K a multiple of 8).  Meant for 17 to 64
+    rows, where the tokens' tile is too large to be fetched again for every 64 weight rows.
+    ``second`` = (a2, w2, bias2) sums another product into the same output (K a multiple of 64 then)."""
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    if out is None:
+        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+    g = _gemm_args(a, w, bias, act, add0, add1, out)
+    if a.shape[0] > STREAM_MAX_ROWS or a.shape[1] % 8:
+        raise KernelError(f"gemm_stream takes up to {STREAM_MAX_ROWS} rows and K a multiple of 8")
+    if second is not None:
+        if a.shape[1] % 64:
+            raise KernelError("gemm_stream takes a second product only behind a K that is a multiple of 64")
+        _second_product(g, a, w, second)
+    fn = _lib("gemm_stream.cu").gl_gemm_stream
+    _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_stream")
+    return out
+
+
+def _few_rows(a, w, bias, act, add0, add1, out_dtype, out, second=None):
+    """The weight-streaming product for up to 64 rows: mma.sync for up to 16, tcgen05 above."""
+    if USE_GEMM_STREAM and a.shape[0] >= STREAM_MIN_ROWS:
+        return gemm_stream(a, w, bias, act, add0, add1, out_dtype, out, second=second)
+    return gemm_skinny(a, w, bias, act, add0, add1, out_dtype, out, second=second)
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
                  add0: Optional[torch.Tensor] = None, add1: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
@@ -770,9 +809,9 @@ def linear_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
             and w2.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a2.shape[1] % 8 == 0):
         if a.shape[0] <= SKINNY_MAX_ROWS:
             if a.shape[1] % 64 == 0:
-                return gemm_skinny(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
+                return _few_rows(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
             if a2.shape[1] % 64 == 0:                  # the product whose K fills whole stages goes first
-                return gemm_skinny(a2, w2, bias2, None, add0, None, torch.float32, out, second=(a, w, bias))
+                return _few_rows(a2, w2, bias2, None, add0, None, torch.float32, out, second=(a, w, bias))
         elif USE_TCGEN05:
             return gemm_tcgen05(a, w, bias, None, add0, None, torch.float32, out, second=(a2, w2, bias2))
     out = linear(a, w, bias, add0=add0, out_dtype=torch.float32, out=out)
@@ -799,7 +838,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     types and sizes.  float32 operands always run the 32-bit CUDA-core product."""
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0:
         if a.shape[0] <= SKINNY_MAX_ROWS:
-            return gemm_skinny(a, w, bias, act, add0, add1, out_dtype, out)
+            return _few_rows(a, w, bias, act, add0, add1, out_dtype, out)
         if USE_TCGEN05:
             return gemm_tcgen05(a, w, bias, act, add0, add1, out_dtype, out)
     return gemm_simt(a, w, bias, act, add0, add1, out_dtype, out)

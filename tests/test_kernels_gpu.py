@@ -249,6 +249,66 @@ def test_gemm_skinny_two_products_one_output(M, N, K1, K2):
     assert (x.double() - want).abs().max() <= 3e-5 * max(1.0, want.abs().max().item())
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 128, 64), (64, 200, 416), (33, 777, 2568), (40, 2560, 2560), (64, 7680, 2560),
+                                   (20, 1000, 200), (64, 64, 8), (31, 2560, 12800)])
+def test_gemm_stream(M, N, K):
+    """The tensor-core weight-streaming product (weights as the 128-row operand) for 17 to 64 rows:
+    every split of K over a cluster, both output types, awkward N and K."""
+    o = ops()
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=1)
+    bias, add0, add1 = rnd(N, seed=2), rnd(M, N, seed=3), rnd(M, N, seed=4)
+    ref = ref_linear(a, w, bias, "gelu_new", add0, add1)
+    chunks = -(-K // 64)
+    for split in (0, 1, 2, 3, 5, 8, 16):
+        if split > chunks:
+            continue
+        got = o.gemm_stream(a, w, bias, "gelu_new", add0, add1, out_dtype=torch.float32, split_k=split)
+        torch.cuda.synchronize()
+        assert o.wait_failures()["libgl_gemm_stream"] == 0, "a bounded wait ran out"
+        err = (got.double() - ref).abs().max().item()
+        assert err <= 2e-3 * max(1.0, ref.abs().max().item()), (split, err)
+    got = o.gemm_stream(a, w, None, None, out_dtype=torch.bfloat16)
+    ref = ref_linear(a, w, None, None, None, None)
+    assert (got.double() - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
+    # the same bits from run to run: the parts are added in rank order
+    again = o.gemm_stream(a, w, None, None, out_dtype=torch.bfloat16)
+    assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize("M,N,K1,K2", [(17, 128, 64, 64), (64, 2560, 2560, 10240), (40, 200, 128, 200), (33, 777, 320, 8)])
+def test_gemm_stream_two_products_one_output(M, N, K1, K2):
+    o = ops()
+    a, w = rnd(M, K1, dtype=torch.bfloat16), rnd(N, K1, dtype=torch.bfloat16, scale=0.05, seed=1)
+    a2, w2 = rnd(M, K2, dtype=torch.bfloat16, seed=5), rnd(N, K2, dtype=torch.bfloat16, scale=0.05, seed=6)
+    bias, bias2, add0 = rnd(N, seed=2), rnd(N, seed=7), rnd(M, N, seed=3)
+    ref = a.double() @ w.double().T + a2.double() @ w2.double().T + bias.double() + bias2.double() + add0.double()
+    for split in (0, 1, 4, 7):
+        out = add0.clone()
+        o.gemm_stream(a, w, bias, None, out, None, torch.float32, out, split_k=split, second=(a2, w2, bias2))
+        torch.cuda.synchronize()
+        assert o.wait_failures()["libgl_gemm_stream"] == 0, "a bounded wait ran out"
+        assert (out.double() - ref).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item()), split
+
+
+def test_gemm_stream_one_weight_stands_out():
+    """One large weight at a far corner (last row tile, last k-block of the second product): every token's
+    output in that column must carry it; a lost tile, stage or part would not."""
+    o = ops()
+    M, N, K1, K2 = 48, 2560 + 40, 2560, 1000
+    a, a2 = rnd(M, K1, dtype=torch.bfloat16), rnd(M, K2, dtype=torch.bfloat16, seed=5)
+    w = torch.zeros(N, K1, dtype=torch.bfloat16, device=DEV)
+    w2 = torch.zeros(N, K2, dtype=torch.bfloat16, device=DEV)
+    w2[N - 1, K2 - 1] = 64.0
+    w[5, 0] = -32.0
+    out = torch.zeros(M, N, device=DEV)
+    o.gemm_stream(a, w, None, None, None, None, torch.float32, out, second=(a2, w2, None))
+    torch.cuda.synchronize()
+    want = torch.zeros(M, N, dtype=torch.float64)
+    want[:, N - 1] = 64.0 * a2[:, K2 - 1].double().cpu()
+    want[:, 5] = -32.0 * a[:, 0].double().cpu()
+    assert torch.equal(out.double().cpu(), want)
+
+
 def test_gemm_skinny_one_weight_stands_out():
     """A single large weight far along K must reach exactly one output."""
     o = ops()
