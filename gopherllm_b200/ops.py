@@ -481,13 +481,14 @@ class _DecodeLayerArgs(Structure):
 
 
 DECODE_LAYER_MAX_ROWS = 64
-# Fewer tokens than this go through the separate kernels, which are faster there (measured on Phi-2's
-# sizes: 10 to 20 % at 1 to 16 tokens, equal at 32, the fused layer 3 to 6 % ahead at 48 and 64).
-DECODE_LAYER_MIN_ROWS = 33
-# ... and steps whose longest sequence is no longer than this: with few pages a sequence the fused
-# layer's per-head start and finish outweigh what it saves (64 sequences of 128 positions: 3.77 against
-# 3.58 ms a step; of 300: 4.30 against 4.40; of 2,048: 9.4 against 9.9).
-DECODE_LAYER_MIN_CONTEXT = 257
+# Fewer tokens than this go through the separate kernels, which are faster there.  Measured on Phi-2's
+# sizes, ms a step of 32 layers, separate kernels against the fused layer: 1 token 1.40 / 1.82, 8 tokens
+# 1.92 / 2.21, 16 tokens 2.46 / 2.72, 17 tokens 2.83 / 2.79, 32 tokens 3.81 / 3.61 (1,024 positions each);
+# 64 tokens of 128 positions 3.54 / 2.69, of 300 4.48 / 3.50, of 2,048 9.60 / 8.46.
+DECODE_LAYER_MIN_ROWS = 17
+# ... and steps whose longest sequence is shorter than this (none: the fused layer is ahead at every
+# context length from 17 tokens on).
+DECODE_LAYER_MIN_CONTEXT = 0
 DECODE_LAYER_MAX_HEAD_DIM = catalog.MAX_HEAD_DIM["decode_layer.cu"]
 USE_DECODE_LAYER = True
 _DECODE_LAYER_KEEP = None          # a dict here receives the work buffers of the last call (for tests)
