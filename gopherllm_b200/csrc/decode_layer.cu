@@ -4,16 +4,19 @@
 // With few tokens a layer is a stream of bytes: its four weight matrices, read once, and the cached
 // keys and values of the live sequences.  Run as separate kernels (norm, projection, attention,
 // feed-forward, last products) every one of them pays its own start and finish, a few microseconds
-// against 5 to 30 of streaming, and HBM idles in between.  Here a layer is one persistent kernel:
-// as many blocks as the machine holds at once (a cooperative launch), each with two warps that do
-// nothing but issue TMA loads into a ring of stages (20 to 32 KB each), in the order the block will
-// need them, and four warps that consume the stages.  The loads of a phase do not wait for the phase
-// before it to end: weights and old cache pages depend on nothing this kernel computes, so the ring
-// keeps filling while the block waits at a barrier.
+// against 5 to 30 of streaming, and HBM idles in between.  Here a layer is one persistent kernel: a
+// block on every SM (a cooperative launch), each block two halves of six warps that share nothing but
+// the launch and a tensor-memory allocation (a kernel that allocates tensor memory gets one block an
+// SM, so what would be two blocks is two halves of one).  A half has two warps that do nothing but
+// issue TMA loads into its ring of stages (20 to 32 KB each), in the order the half will need them,
+// and four warps that consume the stages.  The loads of a phase do not wait for the phase before it
+// to end: weights and old cache pages depend on nothing this kernel computes, so the ring keeps
+// filling while the block waits at a barrier.
 //
-// Measured on Phi-2's sizes (148 SMs, two blocks each): the ring streams at about 5.2 TB/s whatever
-// its depth, the shape of the weight boxes and the work of the consuming warps; a step's barriers
-// (about 3 us each) hide behind the ring's prefetch only in part.
+// Measured on Phi-2's sizes (148 SMs): 64 tokens over 2,040 cached positions take 267 us a layer, the
+// layer's 1.5 GB read once at 5.6 TB/s (attention alone at 6.0); a step's barriers (about 3 us each)
+// hide behind the ring's prefetch only in part.  From 17 tokens on this kernel is faster than the
+// separate kernels, below that slower (they run four blocks an SM on two streams); the caller chooses.
 //
 // Phases, separated by barriers over the whole grid (an arrival counter and a generation word in
 // global memory; every wait is bounded and a wait that runs out sets the library's failure word):
@@ -26,14 +29,18 @@
 //      wait for the barrier behind phase 2)                                          -> x   (f32)
 //
 // Work is cut so that every block streams the same number of bytes whatever the sizes are: a product
-// is a line of (128-row tile, 64-k chunk) units, tile-major, and block c takes units [c*per, (c+1)*per);
-// attention is a line of (sequence, key/value head, page) units cut the same way.
+// is a line of (128-row tile, 64-k chunk) units, tile-major, and block c takes units [c*per, (c+1)*per)
+// (whole tiles where that keeps nine blocks in ten busy; in phase 3, while there are no more tiles than
+// blocks, whole blocks to a tile, each with an equal share of the down part's and of the out part's
+// chunks); the two halves of a block split each of its runs of chunks in two.  Attention is a line of
+// (sequence, key/value head, page) units cut over the halves in the same way.
 //
 // The products run on tcgen05: the 128 weight rows of a tile are the M of the instruction, the tokens
 // (padded to 16, 32 or 64) its N, the accumulator lies in tensor memory; one thread issues the four
 // products of a stage and their completion frees the stage, so the consuming warps do nothing per stage
-// and read the accumulator once per tile.  A tile that spans several blocks: each writes its partial
-// sums to scratch and counts itself in; when all have, every one of them finishes an equal share of the
+// and read the accumulators once per tile: both halves', added as they are read.  A tile that spans
+// several blocks: each writes its partial sums to scratch and counts itself in; when all have, every
+// one of them finishes an equal share of the
 // tile's tokens, adding the partials in the order of the blocks, so the result does not depend on
 // timing and no block is left to add up a whole tile alone.  A sequence's head that spans several
 // blocks is merged by whichever arrives last, again in the blocks' order.  Softmax, norm and the
