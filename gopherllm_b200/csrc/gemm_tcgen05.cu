@@ -481,9 +481,16 @@ GL_API int gl_gemm_tcgen05(const GemmArgs* args, int out_dtype, int bn, cudaStre
             const int c = cands[i];
             if (c == 160 && out_dtype != GL_F32) continue;
             const int tiles = tm * ((g.N + c - 1) / c + (g.wB ? (g.NB + c - 1) / c : 0));
-            // (tiles that will be cut into equal shares are not modelled here: the widest tile that
-            // the rule below picks is also the one that cuts best)
-            const long cost = (long)((tiles + sms - 1) / sms) * (TG_BM + c);
+            long cost = (long)((tiles + sms - 1) / sms) * (TG_BM + c) * 1000;
+            // Fewer tiles than 70 % of the SMs, added onto a 32-bit output: launch_tg cuts them into equal
+            // shares of (tile, k-block) units, so there are no waves; an SM's share of the operand bytes
+            // counts, plus the add-reduction of its part of a tile, which grows with the tile's width
+            // (measured at 2560 x 12800: 128 rows 19 us at width 128 against 22 at 64 and 25 at 256;
+            // 256 rows 26 against 37 and 28; 512 rows 39 at width 256 against 43 at 128).
+            const long k_blocks = (g.K + TG_BK - 1) / TG_BK + (g.a2 ? (g.K2 + TG_BK - 1) / TG_BK : 0);
+            if (out_dtype == GL_F32 && g.add0 == (const float*)g.out && !g.add1 && g.act == GL_ACT_NONE && !g.wB &&
+                tiles * 10 < sms * 7 && (long)tiles * k_blocks >= 8L * sms)
+                cost = (long)tiles * (TG_BM + c) * 1000 / sms + 150L * c;
             if (best < 0 || cost < best) { best = cost; bn = c; }
         }
         // A long product added onto its 32-bit output, many rows, few columns (the second feed-forward

@@ -11,6 +11,29 @@ from ..config.specs import ModelSpec
 from ..parts.base import ParamSpec, build_block, build_norm
 
 
+def _tensor_addresses(part, prefix: str) -> Dict[str, int]:
+    """name -> address (0 for None) of the tensors an object holds as attributes, in lists, tuples and
+    dicts, and inside the parts it holds; names are attribute paths, so equal for equal parts."""
+    out: Dict[str, int] = {}
+
+    def walk(v, name, depth):
+        if isinstance(v, torch.Tensor):
+            out[name] = v.data_ptr()
+        elif isinstance(v, (list, tuple)):
+            for i, u in enumerate(v):
+                walk(u, f"{name}[{i}]", depth)
+        elif isinstance(v, dict):
+            for k, u in v.items():
+                walk(u, f"{name}[{k!r}]", depth)
+        elif hasattr(v, "parameters") and hasattr(v, "load") and depth < 8:
+            for k, u in sorted(vars(v).items()):
+                walk(u, f"{name}.{k}", depth + 1)
+
+    for k, v in sorted(vars(part).items()):
+        walk(v, prefix + k, 0)
+    return out
+
+
 class DecoderModel:
     """Built from a ModelSpec alone.  One block per entry of ``spec.layers``;
     ``spec.schedule`` says which block runs when and on which cache entry, so a
@@ -24,6 +47,7 @@ class DecoderModel:
         self.positions: Optional[torch.Tensor] = None          # learned absolute positions, if the spec has them
         self.head_weight: Optional[torch.Tensor] = None
         self.head_bias: Optional[torch.Tensor] = None
+        self._held: Dict[int, Dict[str, int]] = {}             # layer -> addresses of its tensors (see run)
 
     # -- parameters -------------------------------------------------------
     def parameters(self) -> Dict[str, ParamSpec]:
@@ -53,6 +77,7 @@ class DecoderModel:
                               if k.startswith("final_norm/")})
         self.head_weight = self.embedding if self.spec.tie_embeddings else tensors["head/weight"]
         self.head_bias = tensors.get("head/bias")
+        self._held = {}
 
     @property
     def capturable(self) -> bool:
@@ -112,10 +137,59 @@ class DecoderModel:
         return x
 
     def run(self, x, ctx, cache, start: int, stop: int) -> None:
-        """Runs start..stop-1 of the schedule, updating x in place."""
+        """Runs start..stop-1 of the schedule, updating x in place.
+
+        The layers of a model are mostly the same block with other tensors, and what the host does
+        for one run of a block (the parts' choices, checks, argument records) costs more time than
+        the kernels of a short prompt take.  So the launches of a block's run are recorded, compared
+        with the launches of the next run of an equal block (they must be the same but for the two
+        blocks' own tensors and temporaries), and from the third such run on repeated with that
+        run's tensors in place of the recorded ones.  Runs that fork onto a second stream are left
+        alone: their events are no launches."""
+        repeat = ops.REPEAT_LAYERS and getattr(ctx, "side_stream", None) is None and stop - start > 2
+        kinds: List[list] = []            # [block, writes, view type, tape, pointers, state, tries]
         for e in self.spec.schedule[start:stop]:
             view = cache.view(e.cache, e.writes) if e.cache is not None else None
-            self.blocks[e.layer].forward(x, ctx, view)
+            block = self.blocks[e.layer]
+            if not repeat or not getattr(block, "launches_only", False):
+                block.forward(x, ctx, view)
+                continue
+            ptrs = self._pointers(e.layer, view)
+            kind = next((k for k in kinds if type(k[0]) is type(block) and k[0].spec == block.spec
+                         and k[1] == e.writes and k[2] is type(view)), None)
+            if kind is not None and kind[5] == "repeat":
+                kind[3].repeat(ptrs)
+                continue
+            if kind is not None and kind[5] == "own":
+                block.forward(x, ctx, view)
+                continue
+            tape = ops.LaunchTape().start()
+            try:
+                block.forward(x, ctx, view)
+            finally:
+                tape.stop()
+            if kind is None:
+                kinds.append([block, e.writes, type(view), tape, ptrs, "recorded", 0])
+            elif kind[3].same_as(tape, kind[4], ptrs):
+                kind[3].bind(kind[4])
+                kind[5] = "repeat"
+            else:
+                # (the first run of a step may do what later ones find done: tables of the step's
+                # positions, say; so the later run becomes the one to compare with, a few times)
+                kind[3], kind[4], kind[6] = tape, ptrs, kind[6] + 1
+                if kind[6] >= 3:
+                    kind[5] = "own"
+
+    def _pointers(self, layer: int, view) -> Dict[str, int]:
+        """name -> address of every tensor block ``layer`` holds, and of the cache entry it runs on."""
+        held = self._held.get(layer)
+        if held is None:
+            held = self._held[layer] = _tensor_addresses(self.blocks[layer], "")
+        if view is None:
+            return held
+        ptrs = dict(held)
+        ptrs.update(_tensor_addresses(view, "cache/"))
+        return ptrs
 
     def finish(self, x, ctx) -> torch.Tensor:
         s = self.spec

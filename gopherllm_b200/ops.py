@@ -43,8 +43,152 @@ LAUNCHES = 0       # kernels launched through this module since it was last set 
 def _check(code: int, what: str, kernels: int = 1) -> None:
     global LAUNCHES
     LAUNCHES += kernels
+    if _TAPE is not None and _TAPE.calls and _TAPE.calls[-1][2] is None:
+        _TAPE.calls[-1][2:] = [what, kernels]
     if code != 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, f'error {code}')}")
+
+
+# ---------------------------------------------------------------------------
+# A tape of launches.  The layers of a model are mostly the same block with other tensors; what the
+# host does for one of them (checks, sizes, argument records: some 100 us for a block of five kernels,
+# more than the kernels take for a short prompt) is the same for the next but for a handful of
+# pointers.  So the launches of one block's run can be recorded and repeated for another block of the
+# same shape with that block's tensors in place of the first one's.
+class _StreamArg(c_void_p):
+    """The stream argument of a launch (a repeated launch takes the stream that is current then)."""
+
+
+class LaunchTape:
+    """The launches between ``start()`` and ``stop()``: [function, arguments, name, kernels] each, and
+    the tensors that were allocated for them meanwhile (kept alive: a repeat uses them again)."""
+
+    def __init__(self):
+        self.calls: list = []
+        self.temps: list = []
+        self.slots: list = []
+        self.streams: list = []
+
+    def start(self) -> "LaunchTape":
+        global _TAPE
+        if _TAPE is not None:
+            raise KernelError("a tape of launches is already being recorded")
+        _TAPE = self
+        return self
+
+    def stop(self) -> "LaunchTape":
+        global _TAPE
+        _TAPE = None
+        return self
+
+    def _pointers(self):
+        """Every place a pointer stands: (holder, attribute), a c_void_p argument or a record's field."""
+        for call in self.calls:
+            for a in call[1]:
+                if isinstance(a, _StreamArg):
+                    continue
+                if isinstance(a, c_void_p):
+                    yield a, "value"
+                else:
+                    st = getattr(a, "_obj", None)
+                    if isinstance(st, Structure):
+                        for name, typ in st._fields_:
+                            if typ is c_void_p:
+                                yield st, name
+
+    def bind(self, ptrs: dict) -> None:
+        """``ptrs``: name -> address of the recorded block's tensors.  Finds the places that hold one."""
+        by_ptr: dict = {}
+        for k, v in ptrs.items():
+            if v:
+                by_ptr.setdefault(v, k)
+        self.slots = [(h, attr, by_ptr[getattr(h, attr)]) for h, attr in self._pointers()
+                      if getattr(h, attr) in by_ptr]
+        self.streams = [a for call in self.calls for a in call[1] if isinstance(a, _StreamArg)]
+
+    def same_as(self, other: "LaunchTape", mine: dict, theirs: dict) -> bool:
+        """Whether ``other``, the tape of another block's own run, is this tape with that block's tensors
+        (``theirs``) in place of this one's (``mine``) and its temporaries in place of this one's, and
+        nothing else different: then repeating this tape with a third block's tensors is that block's run."""
+        if mine.keys() != theirs.keys() or len(self.calls) != len(other.calls) or len(self.temps) != len(other.temps):
+            return False
+        to: dict = {}
+        for k, v in mine.items():
+            if bool(v) != bool(theirs[k]) or (v and to.setdefault(v, theirs[k]) != theirs[k]):
+                return False
+        for a, b in zip(self.temps, other.temps):
+            if a.shape != b.shape or a.dtype != b.dtype:
+                return False
+            to[a.data_ptr()] = b.data_ptr()
+
+        def same_pointer(u, v):
+            return (not u and not v) or (bool(u) and to.get(u, u) == v)
+
+        for (f0, a0, w0, k0), (f1, a1, w1, k1) in zip(self.calls, other.calls):
+            if f0 is not f1:
+                return False
+            if w0 != w1 or k0 != k1 or len(a0) != len(a1):
+                return False
+            for u, v in zip(a0, a1):
+                if type(u) is not type(v):
+                    return False
+                if isinstance(u, _StreamArg):
+                    continue
+                if isinstance(u, c_void_p):
+                    if not same_pointer(u.value, v.value):
+                        return False
+                    continue
+                su, sv = getattr(u, "_obj", None), getattr(v, "_obj", None)
+                if isinstance(su, Structure):
+                    if type(su) is not type(sv):
+                        return False
+                    for name, typ in su._fields_:
+                        x, y = getattr(su, name), getattr(sv, name)
+                        if typ is c_void_p:
+                            if not same_pointer(x, y):
+                                return False
+                        elif hasattr(x, "__len__"):
+                            if list(x) != list(y):
+                                return False
+                        elif x != y:
+                            return False
+                elif getattr(u, "value", u) != getattr(v, "value", v):
+                    return False
+        return True
+
+    def repeat(self, ptrs: dict) -> None:
+        """Launch everything again with these tensors in the recorded block's places."""
+        global TAPE_REPEATS
+        TAPE_REPEATS += 1
+        for h, attr, key in self.slots:
+            setattr(h, attr, ptrs[key] or None)
+        if self.streams:
+            cur = _stream().value
+            for a in self.streams:
+                a.value = cur
+        for fn, args, what, kernels in self.calls:
+            _check(_launch(fn, *args), what, kernels)
+
+
+_TAPE: Optional[LaunchTape] = None
+TAPE_REPEATS = 0            # tapes repeated since this was last set to 0
+REPEAT_LAYERS = True        # whether a model repeats the recorded launches of equal blocks (engine/model.py)
+
+
+def _launch(fn, *args) -> int:
+    """Every kernel launch of this module goes through here."""
+    if _TAPE is not None:
+        _TAPE.calls.append([fn, args, None, 1])
+    return fn(*args)
+
+
+def empty(shape, dtype, device) -> torch.Tensor:
+    """Uninitialised memory for a kernel's output (what the kernels' callers allocate with, so that a
+    tape of launches can keep it)."""
+    t = torch.empty(shape, dtype=dtype, device=device)
+    if _TAPE is not None:
+        _TAPE.temps.append(t)
+    return t
 
 
 def dtype_code(t: torch.dtype) -> int:
@@ -58,12 +202,12 @@ def dtype_code(t: torch.dtype) -> int:
 _RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
-def _stream() -> c_void_p:
+def _stream() -> "_StreamArg":
     # (the raw handle straight from the runtime: a step launches a few hundred kernels, and building a
     # Stream object for each costs more host time than a short kernel runs)
     if _RAW_STREAM is not None:
-        return c_void_p(_RAW_STREAM(torch.cuda.current_device()))
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _StreamArg(_RAW_STREAM(torch.cuda.current_device()))
+    return _StreamArg(torch.cuda.current_stream().cuda_stream)
 
 
 def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
@@ -111,10 +255,10 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, scale: float = 1.0,
     V, D = table.shape
     T = tokens.numel()
     if out is None:
-        out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+        out = empty((T, D), torch.float32, table.device)
     _need(out, "out", torch.float32, (T, D))
     fn = _lib("rowwise.cu").gl_embed
-    _check(fn(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
+    _check(_launch(fn, _ptr(table), c_int(dtype_code(table.dtype)), _ptr(tokens), _ptr(out),
               c_int(T), c_int(D), c_int(V), c_float(scale), _stream()), "embed")
     return out
 
@@ -126,7 +270,7 @@ def add_rows(table: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> tor
     N, D = table.shape
     _need(out, "out", torch.float32, (index.numel(), D))
     fn = _lib("rowwise.cu").gl_add_rows
-    _check(fn(_ptr(table), c_int(dtype_code(table.dtype)), _ptr(index), _ptr(out),
+    _check(_launch(fn, _ptr(table), c_int(dtype_code(table.dtype)), _ptr(index), _ptr(out),
               c_int(index.numel()), c_int(D), c_int(N), _stream()), "add_rows")
     return out
 
@@ -135,7 +279,7 @@ def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torc
     """In place on float32 logits: x * scale, then cap * tanh(x / cap) when cap > 0."""
     _need(x, "x", torch.float32)
     fn = _lib("rowwise.cu").gl_scale_softcap
-    _check(fn(_ptr(x), ctypes.c_longlong(x.numel()), c_float(scale), c_float(cap), _stream()), "scale_softcap")
+    _check(_launch(fn, _ptr(x), ctypes.c_longlong(x.numel()), c_float(scale), c_float(cap), _stream()), "scale_softcap")
     return x
 
 
@@ -154,10 +298,10 @@ def norm(x: torch.Tensor, gamma: torch.Tensor, beta: Optional[torch.Tensor], eps
     else:
         R = x.numel() // D
     if out is None:
-        out = torch.empty((R, D), dtype=out_dtype, device=x.device)
+        out = empty((R, D), out_dtype, x.device)
     _need(out, "out", out_dtype, (R, D))
     fn = _lib("rowwise.cu").gl_norm
-    _check(fn(_ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), c_int(dtype_code(out_dtype)),
+    _check(_launch(fn, _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out), c_int(dtype_code(out_dtype)),
               c_int(R), c_int(D), c_float(eps), c_int(1 if rms else 0), _stream()), "norm")
     return out
 
@@ -174,7 +318,7 @@ def advance_decode(tokens, tok_pos, seq_ctx, sampled, history, counter) -> None:
     if sampled.numel() < B or history.shape[-1] != B:
         raise KernelError("advance_decode: sampled or history does not match the batch")
     fn = _lib("rowwise.cu").gl_advance_decode
-    _check(fn(_ptr(tokens), _ptr(tok_pos), _ptr(seq_ctx), _ptr(sampled), _ptr(history), _ptr(counter),
+    _check(_launch(fn, _ptr(tokens), _ptr(tok_pos), _ptr(seq_ctx), _ptr(sampled), _ptr(history), _ptr(counter),
               c_int(B), c_int(history.shape[0]), _stream()), "advance_decode")
 
 
@@ -183,10 +327,10 @@ def rope_table(pos: torch.Tensor, inv_freq: torch.Tensor):
     _need(pos, "pos", torch.int32)
     _need(inv_freq, "inv_freq", torch.float32)
     T, half = pos.numel(), inv_freq.numel()
-    cosv = torch.empty((T, half), dtype=torch.float32, device=pos.device)
-    sinv = torch.empty_like(cosv)
+    cosv = empty((T, half), torch.float32, pos.device)
+    sinv = empty(cosv.shape, cosv.dtype, cosv.device)
     fn = _lib("qkv_cache.cu").gl_rope_table
-    _check(fn(_ptr(pos), _ptr(inv_freq), _ptr(cosv), _ptr(sinv), c_int(T), c_int(half), _stream()),
+    _check(_launch(fn, _ptr(pos), _ptr(inv_freq), _ptr(cosv), _ptr(sinv), c_int(T), c_int(half), _stream()),
            "rope_table")
     return cosv, sinv
 
@@ -248,7 +392,7 @@ def qkv_to_cache(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, 
                       1 if interleaved else 0, 1 if norm_rms else 0, 1 if write_kv else 0,
                       norm_eps, q_scale, k_cache.shape[0])
     fn = _lib("qkv_cache.cu").gl_qkv_cache
-    _check(fn(byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+    _check(_launch(fn, byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "qkv_to_cache")
 
 
@@ -293,7 +437,7 @@ def attention_generic(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, p
     a = _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
                    num_heads, num_kv_heads, head_dim, window, max_qlen, score_scale)
     fn = _lib("attention_generic.cu").gl_attention_generic
-    _check(fn(byref(a), c_int(dtype_code(q.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
+    _check(_launch(fn, byref(a), c_int(dtype_code(q.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "attention_generic")
 
 
@@ -309,7 +453,7 @@ def attention_prefill(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, p
     a = _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
                    num_heads, num_kv_heads, head_dim, window, max_qlen, 1.0)
     lib = _lib("attention_prefill.cu", catalog.head_dim_defines(head_dim))
-    _check(lib.gl_attention_prefill(byref(a), _stream()), "attention_prefill")
+    _check(_launch(lib.gl_attention_prefill, byref(a), _stream()), "attention_prefill")
 
 
 def attention_prefill_tc(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
@@ -325,7 +469,7 @@ def attention_prefill_tc(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx
     a = _attn_args(q, out, k_cache, v_cache, seq_qstart, seq_qlen, seq_ctx, pages,
                    num_heads, num_kv_heads, head_dim, window, max_qlen, 1.0)
     lib = _lib("attention_prefill_tc.cu", catalog.head_dim_defines(head_dim))
-    _check(lib.gl_attention_prefill_tc(byref(a), c_int(q.shape[0]), c_int(k_cache.shape[0]), _stream()),
+    _check(_launch(lib.gl_attention_prefill_tc, byref(a), c_int(q.shape[0]), c_int(k_cache.shape[0]), _stream()),
            "attention_prefill_tc")
 
 
@@ -426,7 +570,7 @@ def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, n
     if splits > 8 or (splits > 1 and scratch is not None):
         n_o, n_ml = B * num_heads * splits * head_dim, B * num_heads * splits * 2
         if scratch is None:
-            scratch = torch.empty(n_o + n_ml, dtype=torch.float32, device=out.device)
+            scratch = empty(n_o + n_ml, torch.float32, out.device)
         _need(scratch, "scratch", torch.float32)
         if scratch.numel() < n_o + n_ml:
             raise KernelError("decode attention scratch is too small")
@@ -436,11 +580,11 @@ def attention_decode(q, out, k_cache, v_cache, seq_ctx, pages, num_heads: int, n
                     B, num_heads, num_kv_heads, pages.shape[-1], window, splits)
     launches = 2 if part_o is not None else 1
     if qkv is None:
-        _check(lib.gl_attention_decode(byref(a), _stream()), "attention_decode", launches)
+        _check(_launch(lib.gl_attention_decode, byref(a), _stream()), "attention_decode", launches)
     else:
         x = _DecodeQkv(qkv.data_ptr(), _addr(cos), _addr(sin), cos.shape[1] if cos is not None else 0,
                        int(bool(write_kv)), float(q_scale))
-        _check(lib.gl_attention_decode_qkv(byref(a), byref(x), _stream()), "attention_decode", launches)
+        _check(_launch(lib.gl_attention_decode_qkv, byref(a), byref(x), _stream()), "attention_decode", launches)
 
 
 def attention(q, out, k_cache, v_cache, ctx, pages, num_heads: int, num_kv_heads: int,
@@ -557,10 +701,10 @@ def decode_layer(x: torch.Tensor, norm_g: torch.Tensor, norm_b: Optional[torch.T
     dev = x.device
     lib = _lib("decode_layer.cu", catalog.head_dim_defines(head_dim))
     bf = torch.bfloat16
-    xn = torch.empty((M, D), dtype=bf, device=dev)
-    qkv = torch.empty((M, Nqkv), dtype=bf, device=dev)
-    o = torch.empty((M, No), dtype=bf, device=dev)
-    h = torch.empty((M, I), dtype=bf, device=dev)
+    xn = empty((M, D), bf, dev)
+    qkv = empty((M, Nqkv), bf, dev)
+    o = empty((M, No), bf, dev)
+    h = empty((M, I), bf, dev)
     a = _DecodeLayerArgs(x.data_ptr(), norm_g.data_ptr(), _addr(norm_b), w_qkv.data_ptr(), _addr(b_qkv),
                          w_up.data_ptr(), _addr(b_up), w_out.data_ptr(), _addr(b_out), w_down.data_ptr(), _addr(b_down),
                          k_cache.data_ptr(), v_cache.data_ptr(), pages.data_ptr(), seq_ctx.data_ptr(),
@@ -577,9 +721,9 @@ def decode_layer(x: torch.Tensor, norm_g: torch.Tensor, norm_b: Optional[torch.T
                               "run the step once outside it")
         # zero once; every call leaves the counters zero again (the generation word only ever grows)
         sync = _DECODE_LAYER_SYNC[idx] = torch.zeros(max(int(n_sync.value), 1 << 16), dtype=torch.int32, device=dev)
-    scratch = torch.empty(max(1, int(n_scratch.value)), dtype=torch.float32, device=dev)
+    scratch = empty(max(1, int(n_scratch.value)), torch.float32, dev)
     a.scratch, a.sync = scratch.data_ptr(), sync.data_ptr()
-    _check(lib.gl_decode_layer(byref(a), _stream()), "decode_layer")
+    _check(_launch(lib.gl_decode_layer, byref(a), _stream()), "decode_layer")
     if _DECODE_LAYER_KEEP is not None:
         _DECODE_LAYER_KEEP.update(xn=xn, qkv=qkv, o=o, h=h)
     return x
@@ -627,10 +771,10 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
               out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = act(a · wᵀ + bias) + add0 + add1 on CUDA cores in 32-bit (any element type, any size)."""
     if out is None:
-        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+        out = empty((a.shape[0], w.shape[0]), out_dtype or a.dtype, a.device)
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     fn = _lib("gemm_simt.cu").gl_gemm_simt
-    _check(fn(byref(g), c_int(dtype_code(a.dtype)), c_int(dtype_code(w.dtype)),
+    _check(_launch(fn, byref(g), c_int(dtype_code(a.dtype)), c_int(dtype_code(w.dtype)),
               c_int(dtype_code(out.dtype)), _stream()), "gemm_simt")
     return out
 
@@ -668,7 +812,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     if out is None:
-        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+        out = empty((a.shape[0], w.shape[0]), out_dtype or a.dtype, a.device)
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[0] > SKINNY_MAX_ROWS or a.shape[1] % 8:
         raise KernelError(f"gemm_skinny takes up to {SKINNY_MAX_ROWS} rows and K a multiple of 8")
@@ -677,7 +821,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
             raise KernelError("gemm_skinny takes a second product only behind a K that is a multiple of 64")
         _second_product(g, a, w, second)
     fn = _lib("gemm_skinny.cu").gl_gemm_skinny
-    _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_skinny")
+    _check(_launch(fn, byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_skinny")
     return out
 
 
@@ -700,7 +844,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     if out is None:
-        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+        out = empty((a.shape[0], w.shape[0]), out_dtype or a.dtype, a.device)
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[0] > STREAM_MAX_ROWS or a.shape[1] % 8:
         raise KernelError(f"gemm_stream takes up to {STREAM_MAX_ROWS} rows and K a multiple of 8")
@@ -709,7 +853,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] =
             raise KernelError("gemm_stream takes a second product only behind a K that is a multiple of 64")
         _second_product(g, a, w, second)
     fn = _lib("gemm_stream.cu").gl_gemm_stream
-    _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_stream")
+    _check(_launch(fn, byref(g), c_int(dtype_code(out.dtype)), c_int(split_k), _stream()), "gemm_stream")
     return out
 
 
@@ -733,7 +877,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     _need(a, "a", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     if out is None:
-        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype or a.dtype, device=a.device)
+        out = empty((a.shape[0], w.shape[0]), out_dtype or a.dtype, a.device)
     g = _gemm_args(a, w, bias, act, add0, add1, out)
     if a.shape[1] % 8:
         raise KernelError("gemm_tcgen05 takes K a multiple of 8 (TMA needs 16-byte row pitch)")
@@ -747,13 +891,13 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
             raise KernelError(f"second set of columns {tuple(w_b.shape)} does not fit a {tuple(a.shape)}")
         if bias_b is not None:
             _need(bias_b, "biasB", torch.float32, (w_b.shape[0],))
-        out_b = torch.empty((a.shape[0], w_b.shape[0]), dtype=out.dtype, device=a.device)
+        out_b = empty((a.shape[0], w_b.shape[0]), out.dtype, a.device)
         g.wB, g.biasB, g.outB, g.NB, g.actB = w_b.data_ptr(), _addr(bias_b), out_b.data_ptr(), w_b.shape[0], ACTIVATIONS[act_b]
     if tile_n not in (0, 64, 128, 160, 192, 256, 1160, 1192, 1256):
         raise KernelError("tile_n is 0 (choose), 64, 128, 160 (32-bit output only), 192 or 256; "
                           "1000 more for tiles of 256 rows (160, 192, 256)")
     fn = _lib("gemm_tcgen05.cu", _defines).gl_gemm_tcgen05
-    _check(fn(byref(g), c_int(dtype_code(out.dtype)), c_int(tile_n), _stream()), "gemm_tcgen05")
+    _check(_launch(fn, byref(g), c_int(dtype_code(out.dtype)), c_int(tile_n), _stream()), "gemm_tcgen05")
     return out if fork is None else (out, out_b)
 
 
@@ -909,8 +1053,8 @@ def sample(logits: torch.Tensor, work: torch.Tensor, recent: torch.Tensor, recen
     if needs_sort_scratch(temperature, top_k, top_p, min_p, V):
         vpad = sort_scratch_size(V)
         if sort_key is None:
-            sort_key = torch.empty((B, vpad), dtype=torch.float32, device=logits.device)
-            sort_idx = torch.empty((B, vpad), dtype=torch.int32, device=logits.device)
+            sort_key = empty((B, vpad), torch.float32, logits.device)
+            sort_idx = empty((B, vpad), torch.int32, logits.device)
         _need(sort_key, "sort_key", torch.float32)
         _need(sort_idx, "sort_idx", torch.int32)
         if sort_key.numel() < B * vpad or sort_idx.numel() < B * vpad:
@@ -919,7 +1063,7 @@ def sample(logits: torch.Tensor, work: torch.Tensor, recent: torch.Tensor, recen
                     recent_n.data_ptr(), rng.data_ptr(), out.data_ptr(), _addr(sort_key), _addr(sort_idx),
                     B, V, vpad, top_k,
                     temperature, top_p, min_p, repeat_penalty)
-    _check(_lib("sampling.cu").gl_sample(byref(a), _stream()), "sample")
+    _check(_launch(_lib("sampling.cu").gl_sample, byref(a), _stream()), "sample")
 
 
 def set_pdl(on: bool) -> None:

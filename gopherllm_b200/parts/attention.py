@@ -19,6 +19,7 @@ class Attention(Mixer):
 
     deferred_add = True
     capturable = True
+    launches_only = True
 
     def __init__(self, spec: MixerSpec):
         if spec.num_heads % spec.num_kv_heads:
@@ -108,13 +109,13 @@ class Attention(Mixer):
                                          s.position.interleaved, self.q_norm is not None)):
             # one token a sequence: attention reads the projection's output itself (rotation, query scale
             # and the cache write happen inside it), one kernel less between two products
-            o = torch.empty((T, s.num_heads * s.head_dim), dtype=ctx.act_dtype, device=xn.device)
+            o = ops.empty((T, s.num_heads * s.head_dim), ctx.act_dtype, xn.device)
             splits = ops.decode_splits(ctx.n_seqs, s.num_kv_heads, ctx.max_len, xn.device, s.head_dim, group)
             ops.attention_decode(None, o, cache.k, cache.v, ctx.seq_ctx, pages, s.num_heads, s.num_kv_heads,
                                  s.head_dim, splits, s.window, qkv=qkv, cos=cos, sin=sin, q_scale=s.q_scale,
                                  write_kv=cache.writes)
             return o, self.w_out, self.b_out
-        q = torch.empty((T, s.num_heads * s.head_dim), dtype=ctx.act_dtype, device=xn.device)
+        q = ops.empty((T, s.num_heads * s.head_dim), ctx.act_dtype, xn.device)
         qn = kn = None
         eps, rms = 0.0, False
         if self.q_norm is not None:
@@ -124,7 +125,7 @@ class Attention(Mixer):
                          s.num_heads, s.num_kv_heads, s.head_dim, s.q_scale, cos, sin,
                          interleaved=s.position.interleaved, q_norm=qn, k_norm=kn,
                          norm_eps=eps, norm_rms=rms, write_kv=cache.writes)
-        o = torch.empty_like(q)
+        o = ops.empty(q.shape, q.dtype, q.device)
         ops.attention(q, o, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads,
                       s.head_dim, window=s.window)
         return o, self.w_out, self.b_out

@@ -55,8 +55,15 @@ class Part:
     capturable: True if ``forward`` only launches work on the current stream (no copy to
     the host, no host-side decision on device data), so a step can be recorded into a
     CUDA graph.  The default is False: a part must opt in.
+
+    launches_only: True if everything ``forward`` does on the device is a launch through
+    ``gopherllm_b200.ops`` (no torch operation, no copy, no second stream) with memory from
+    ``ops.empty``, and what it does on the host does not depend on which of several equal parts
+    it is.  A model repeats the recorded launches of such a block for the next equal block
+    instead of walking through its parts again.  The default is False: a part must opt in.
     """
     capturable = False
+    launches_only = False
 
     def parameters(self) -> Dict[str, ParamSpec]:
         return {}

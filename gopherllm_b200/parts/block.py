@@ -51,6 +51,10 @@ class AssembledBlock(Block):
     def capturable(self):
         return all(part.capturable for part in self.children().values())
 
+    @property
+    def launches_only(self):
+        return all(part.launches_only for part in self.children().values())
+
 
 class ParallelBlock(AssembledBlock):
     """x ← (x + ffn(n)) + mixer(n), n = norm(x): one norm feeds both branches
@@ -125,7 +129,7 @@ class ParallelBlock(AssembledBlock):
         # start and finish, and nothing of the feed-forward is left on the path from one layer's
         # norm to the next.  The sum is the same three terms in 32-bit, added as (attn + x) + mlp.
         main = torch.cuda.current_stream()
-        y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        y = ops.empty(x.shape, torch.float32, x.device)
         fork, join = torch.cuda.Event(), torch.cuda.Event()
         fork.record(main)
         side.wait_event(fork)

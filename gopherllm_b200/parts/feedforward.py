@@ -15,6 +15,7 @@ class DenseFeedForward(FeedForward):
     forward_batch.go:537-581).  The activation runs in the first product's
     epilogue, the additions to the residual in the second's."""
     capturable = True
+    launches_only = True
 
     def __init__(self, spec: FeedForwardSpec):
         if spec.activation not in ops.ACTIVATIONS:

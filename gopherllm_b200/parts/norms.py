@@ -14,6 +14,7 @@ class LayerNorm(Norm):
     """y = (x - mean) * rsqrt(var + eps) * weight + bias, biased variance, in
     32-bit with the reciprocal square root in 64-bit (bert.go:748-776)."""
     capturable = True
+    launches_only = True
     rms = False
 
     def __init__(self, spec: NormSpec):

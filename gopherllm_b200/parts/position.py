@@ -26,6 +26,7 @@ class Rope(PositionEncoding):
     in 64-bit (prepareRopeScratch, model.go:3041-3046).  The tables depend on
     the step's positions only, so every layer of a step shares them."""
     capturable = True
+    launches_only = True
 
     def __init__(self, spec: PositionSpec):
         if spec.rotary_dim % 2:
@@ -47,6 +48,7 @@ class Rope(PositionEncoding):
 
 class NoPosition(PositionEncoding):
     capturable = True
+    launches_only = True
     def __init__(self, spec: PositionSpec):
         self.spec = spec
 

@@ -342,3 +342,51 @@ def test_forty_sequences_take_the_fused_decode_layer_by_default():
         m.close_sequence(s)
     m.engine.cache.check()
     m.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_later_layers_repeat_the_recorded_launches_of_an_equal_layer(dtype):
+    """Six equal layers.  A step records the launches of a layer, compares them with the next layer's
+    and repeats them for the rest with those layers' tensors.  The logits must be bit for bit what the
+    step gives when every layer walks through its parts, for prompts of unequal lengths in one step and
+    for the single-token steps behind them, and they must agree with the plain implementation."""
+    import gopherllm_b200 as gl
+    from gopherllm_b200 import ops
+    cfg = tiny.TINY["E"][0]
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(23)
+    seqs = [tiny.prompt(rng, n, V) for n in (37, 8, 70)]
+    lens = [30, 2, 64]
+
+    def run(repeat):
+        ops.REPEAT_LAYERS = repeat
+        ops.TAPE_REPEATS = 0
+        m = gl.load(tiny.folder("E"), dtype=dtype, max_tokens=3 * 128)
+        m.engine.use_graphs = False                        # single-token steps launch their kernels too,
+        m.engine.overlap_branches = False                  # on one stream (a fork onto a second one is not repeated)
+        slots = [m.open_sequence() for _ in seqs]
+        outs = [m.step([(slots[i], seqs[i][:lens[i]]) for i in range(3)], [list(range(n)) for n in lens]).clone()]
+        for step in range(5):
+            outs.append(m.step([(slots[i], [seqs[i][lens[i] + step]]) for i in range(3)]).clone())
+        for s in slots:
+            m.close_sequence(s)
+        m.engine.check_device()
+        m.close()
+        return outs, ops.TAPE_REPEATS
+
+    try:
+        own, none = run(False)
+        rep, count = run(True)
+    finally:
+        ops.REPEAT_LAYERS = True
+    assert none == 0
+    assert count >= 6 * 3, f"only {count} repeats in six steps of six layers"
+    for a, b in zip(own, rep):
+        assert torch.equal(a, b)
+    for i in range(3):
+        ref = plain_logits("E", seqs[i])
+        err, bound = tiny.close(rep[0][sum(lens[:i]):sum(lens[:i + 1])].cpu().numpy(), ref[:lens[i]], dtype)
+        assert err <= bound, (i, err, bound)
+        for step in range(5):
+            err, bound = tiny.close(rep[1 + step][i].cpu().numpy(), ref[lens[i] + step], dtype)
+            assert err <= bound, (i, step, err, bound)

@@ -120,3 +120,5 @@ TINY_D = dict(architectures=["PhiForCausalLM"], model_type="phi", num_hidden_lay
               hidden_act="gelu_new", qk_layernorm=False, tie_word_embeddings=False,
               max_position_embeddings=320, initializer_range=0.05, torch_dtype="bfloat16", eos_token_id=3)
 TINY["D"] = (TINY_D, 6)
+# six equal layers: enough for a step to repeat the recorded launches of one layer for the later ones
+TINY["E"] = (dict(TINY_C, num_hidden_layers=6), 8)
