@@ -722,6 +722,8 @@ def test_sampling_matches_plain(V):
     (64, 2, 1, 128, 256, 256, 0, 0, False, "gelu", True),         # the largest head and batch, no rotation
     (17, 6, 3, 48, 288, 200, 48, 0, False, "gelu_new", True),     # head size 48, a fully rotated head
     (1, 32, 32, 80, 2560, 10240, 32, 0, False, "gelu_new", True), # one token at Phi-2's sizes
+    (64, 32, 32, 80, 2560, 10240, 32, 0, False, "gelu_new", True),  # 64 tokens at Phi-2's sizes: whole tiles to a block, seven blocks a tile in the last product
+    (24, 8, 8, 80, 1032, 4104, 32, 0, False, "gelu_new", True),   # 24 tokens (padded to 32), widths that end inside a chunk
 ])
 def test_decode_layer(M, nH, nKV, hd, D, I, rot, window, rms, act, bias):
     """norm -> (attention over the paged cache | feed-forward) -> residual sum as one kernel, against the
