@@ -6,7 +6,9 @@ row of every state tensor.  Cache entries whose mixers ask for the same shape
 (key/value heads, head size, window) form a group with storage and a page pool
 of its own; a model whose layers differ (all keys here, a window there, state
 elsewhere) gets several groups.  When a sequence ends its slot and pages go back
-to the pools and are handed to the next sequence without being cleared:
+to the pools and are handed to the next sequence without being cleared;
+a group whose mixers see a window of the last w positions gives a sequence's
+pages back as soon as they lie wholly before every window still to come:
 positions past a sequence's length are never read (the reference's argument for
 not clearing its cache, runtime.go:1530-1531), and state rows are zeroed when a
 slot is taken (runtime.go:1526-1539).
@@ -26,6 +28,7 @@ from ..parts.base import KVRequest, StateRequest
 from .pool import CacheFull, IdPool
 
 PAGE = 64
+RELEASED = -1        # in a sequence's list of pages: this one lay before the window and went back to the pool
 
 
 @dataclass
@@ -100,6 +103,8 @@ class SequenceCache:
         # per-slot bookkeeping
         self._length = [0] * self.max_slots
         self._pages: List[List[List[int]]] = [[[] for _ in self.groups] for _ in range(self.max_slots)]
+        # per slot and group: pages before this index have been released (groups with a window only)
+        self._first_page: List[List[int]] = [[0 for _ in self.groups] for _ in range(self.max_slots)]
 
     # -- sizes ------------------------------------------------------------
     def bytes(self) -> int:
@@ -183,24 +188,40 @@ class SequenceCache:
                 self._pages[slot][g.gid].extend(g.pool.take_many(k))
 
     def commit(self, slot: int, new_len: int) -> None:
-        """Record that positions up to new_len are now written."""
+        """Record that positions up to new_len are now written.  In a group with a window w the next
+        token (at position new_len) sees keys from new_len - w + 1 on and every later token later ones,
+        so pages that end before that position are given back at once: a long sequence holds about
+        w / 64 + 1 pages of such a group, not all of its positions."""
         self._held(slot)
         if -(-new_len // PAGE) > (len(self._pages[slot][0]) if self.groups else new_len):
             raise ValueError(f"slot {slot}: length {new_len} was not reserved")
         self._length[slot] = new_len
+        for g in self.groups:
+            w = g.req.window
+            if w > 0:
+                pg = self._pages[slot][g.gid]
+                keep_from = min(max(0, new_len - w + 1) // PAGE, len(pg))
+                for i in range(self._first_page[slot][g.gid], keep_from):
+                    g.pool.give(pg[i])
+                    pg[i] = RELEASED
+                if keep_from > self._first_page[slot][g.gid]:
+                    self._first_page[slot][g.gid] = keep_from
 
     def close(self, slot: int) -> None:
         """Give back a sequence's pages and slot."""
         self._held(slot)
         for g in self.groups:
             for p in self._pages[slot][g.gid]:
-                g.pool.give(p)
+                if p != RELEASED:
+                    g.pool.give(p)
             self._pages[slot][g.gid] = []
+            self._first_page[slot][g.gid] = 0
         self._length[slot] = 0
         self.slots.give(slot)
 
     def page_rows(self, group: int, slots: Sequence[int], out: Optional[np.ndarray] = None) -> np.ndarray:
-        """[len(slots), max_pages_per_seq] int32 page ids (unused tail 0)."""
+        """[len(slots), max_pages_per_seq] int32 page ids (the unused tail and pages released before a
+        window are 0: no kernel reads them)."""
         if out is None:
             out = np.zeros((len(slots), self.max_pages_per_seq), dtype=np.int32)
         else:
@@ -208,6 +229,9 @@ class SequenceCache:
         for r, slot in enumerate(slots):
             pg = self._pages[slot][group]
             out[r, :len(pg)] = pg
+            k = self._first_page[slot][group]
+            if k:
+                out[r, :k] = 0
         return out
 
     def live_slots(self) -> List[int]:
@@ -229,6 +253,9 @@ class SequenceCache:
                 pg = self._pages[s][g.gid]
                 if not self.slots.is_held(s):
                     assert not pg, f"free slot {s} still owns pages"
-                owned.extend(pg)
+                k = self._first_page[s][g.gid]
+                assert all(p == RELEASED for p in pg[:k]) and all(p != RELEASED for p in pg[k:]), \
+                    f"slot {s}: released pages of group {g.gid} do not form the head of its list"
+                owned.extend(pg[k:])
             assert len(owned) == len(set(owned)), f"a page of group {g.gid} is owned twice"
             assert len(owned) == g.pool.held_count, f"pages of group {g.gid} are lost"

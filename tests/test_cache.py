@@ -115,3 +115,35 @@ def test_state_rows_are_zeroed_when_a_slot_is_taken():
     s2 = c.open()
     assert s2 == s and float(v.rows[s2].abs().sum()) == 0.0
     assert c.view(5) is None
+
+
+def test_pages_before_a_window_go_back_as_the_sequence_grows():
+    """Group 1 of ``make`` sees the last 128 positions.  Once a page lies wholly before the window of the
+    next token it is free again (and reused by another sequence), while the group that sees every
+    position keeps all of its pages; the table handed to the kernels shows 0 in a released place."""
+    c = make(max_tokens=64 * 14, max_positions=64 * 9, slots=3)
+    a = c.open()
+    c.reserve([(a, 500)])
+    assert c.groups[1].pool.held_count == 8            # a whole prompt needs all its pages while it runs
+    c.commit(a, 500)
+    # the next token, at 500, sees 373..500: pages 0..4 (positions 0..319) lie before that
+    assert c._first_page[a][1] == 5 and c.groups[1].pool.held_count == 3 and c.groups[0].pool.held_count == 8
+    rows = c.page_rows(1, [a])
+    assert list(rows[0][:5]) == [0] * 5 and all(int(p) == q for p, q in zip(rows[0][5:8], c._pages[a][1][5:8]))
+    assert list(c.page_rows(0, [a])[0][:8]) == c._pages[a][0]
+    c.check()
+    b = c.open()
+    c.reserve([(b, 64 * 5)])                           # takes the pages group 1 got back
+    assert set(c._pages[b][1]) == {0, 1, 2, 3, 4}
+    c.commit(b, 64 * 5)
+    c.check()
+    for n in range(501, 577):                          # token by token: a page goes back each time the window passes one
+        c.reserve([(a, n)])
+        c.commit(a, n)
+        assert c._first_page[a][1] == (n - 127) // PAGE
+        c.check()
+    assert len(c._pages[a][1]) == 9 and c.groups[1].pool.held_count == (9 - 7) + (5 - 3)
+    c.close(a)
+    c.close(b)
+    c.check()
+    assert all(g.pool.free_count == g.pool.n for g in c.groups)
