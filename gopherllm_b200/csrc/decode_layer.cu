@@ -171,17 +171,29 @@ __device__ __forceinline__ float dl_cons_sum(float v, float* red, int tid, int b
 // sums v[e].  phase 1: bias, activation on the up part, bfloat16 into qkv or h.  phase 3: both biases and
 // the residual, 32-bit, onto x.  Everything the row needs from memory is loaded before the first store, so
 // the loads overlap.  The threads of a warp hold neighbouring weight rows: a store of theirs is one line.
+// `b` is the row's bias (dl_row_bias), which the caller asks for before the sums are ready.
+__device__ __forceinline__ float dl_row_bias(const LayerArgs& a, int phase, int tile, int nl) {
+    const DecodeLayerArgs& p = a.p;
+    if (phase == 1) {
+        const bool up = tile >= a.tiles_q;
+        const int n = (up ? tile - a.tiles_q : tile) * DL_ROWS + nl;
+        const float* bias = up ? p.b_up : p.b_qkv;
+        return (bias && n < (up ? p.I : a.Nqkv)) ? bias[n] : 0.f;
+    }
+    const int n = tile * DL_ROWS + nl;
+    if (n >= p.D) return 0.f;
+    return (p.b_out ? p.b_out[n] : 0.f) + (p.b_down ? p.b_down[n] : 0.f);
+}
+
 template <int NE>
 __device__ __forceinline__ void dl_finish_rows(const LayerArgs& a, int phase, int tile, int nl, int m0, int mend,
-                                               const float (&v)[NE]) {
+                                               const float (&v)[NE], float b) {
     const DecodeLayerArgs& p = a.p;
     if (phase == 1) {
         const bool up = tile >= a.tiles_q;
         const int n = (up ? tile - a.tiles_q : tile) * DL_ROWS + nl;
         const int N = up ? p.I : a.Nqkv;
         if (n >= N) return;
-        const float* bias = up ? p.b_up : p.b_qkv;
-        const float b = bias ? bias[n] : 0.f;
         __nv_bfloat16* out = (__nv_bfloat16*)(up ? p.h : p.qkv);
 #pragma unroll
         for (int e = 0; e < NE; ++e) {
@@ -193,7 +205,6 @@ __device__ __forceinline__ void dl_finish_rows(const LayerArgs& a, int phase, in
     } else {
         const int n = tile * DL_ROWS + nl;
         if (n >= p.D) return;
-        const float b = (p.b_out ? p.b_out[n] : 0.f) + (p.b_down ? p.b_down[n] : 0.f);
         float xs[NE];
 #pragma unroll
         for (int e = 0; e < NE; ++e) xs[e] = m0 + e < mend ? __ldcg(p.x + (size_t)(m0 + e) * p.D + n) : 0.f;
@@ -519,6 +530,8 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
             int q0, q1;
             my_part(n1 + n2, q0, q1);
             const int n_my = q1 - q0;
+            // (asked for now, while the products run: a layer's biases are cold in a decode step)
+            const float row_bias = nseg == 1 ? dl_row_bias(a, phase, tile, nl) : 0.f;
             if (warp == 0) {
                 if (lane == 0) {
                     int s_ = slot, l_ = lap;
@@ -556,7 +569,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
 #pragma unroll
                 for (int e = 0; e < CH; ++e) v[e] = __uint_as_float(r0[e]) + (two ? __uint_as_float(r1[e]) : 0.f);
                 if (nseg == 1) {
-                    dl_finish_rows<CH>(a, phase, tile, nl, half * CH, p.M, v);
+                    dl_finish_rows<CH>(a, phase, tile, nl, half * CH, p.M, v, row_bias);
                 } else {
                     float* mine = scratch + ((size_t)tile * maxseg + ord) * SZ;
 #pragma unroll
@@ -577,6 +590,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
         // block delivers all its parts before it waits for anyone's, and all blocks are resident, so the waits end.
         for (int q = 0; q < npend; ++q) {
             const int tile = pend_tile[q], nseg = pend_nseg[q], ord = pend_ord[q];
+            const float row_bias = dl_row_bias(a, phase, tile, nl);      // (under the wait for the other blocks)
             if (threadIdx.x == 0 && !dead) {
                 bool ok = false;
                 for (unsigned i = 0; i < GL_SPIN_LIMIT && !ok; ++i) ok = (int)dl_ld_acquire((const unsigned*)cnt + tile) >= nseg;
@@ -604,7 +618,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
 #pragma unroll
                         for (int e = 0; e < 8; ++e) v[e] += t4[u][e];
                 }
-                dl_finish_rows<8>(a, phase, tile, nl, m0, r1, v);
+                dl_finish_rows<8>(a, phase, tile, nl, m0, r1, v, row_bias);
             }
             both_sync();
             if (threadIdx.x == 0 && atomicAdd(done + tile, 1) == nseg - 1) {     // the last to finish leaves both as the next call expects them

@@ -106,9 +106,31 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
     gl_grid_launch_dependents();
     if (tid == 0)
         for (int s = 0; s < STAGES - 1 && s < iters; ++s) load_w(s);
+    // What the epilogue adds is asked for now, not when the sums are ready: the biases (this thread
+    // finishes elements of one column only, since the threads of a block are a multiple of the columns a
+    // block finishes) before the wait, the residual values behind it.  In a decode step both are cold or
+    // far, and their trip would otherwise follow the products instead of running under them.
+    const int cnt = SK_ROWS / S;
+    const int my_n = n0 + rank * cnt + tid % cnt;
+    float my_bias = 0.f;
+    if (my_n < g.N) {
+        if (g.bias) my_bias = g.bias[my_n];
+        if (g.bias2) my_bias += g.bias2[my_n];
+    }
     gl_grid_wait();
     if (tid == 0)
         for (int s = 0; s < STAGES - 1 && s < iters; ++s) load_a(s);
+    constexpr int EARLY = MT <= 2 ? MT * 4 : 1;               // elements a thread finishes at most (few rows only)
+    float early0[EARLY], early1[EARLY];
+    if constexpr (MT <= 2) {
+#pragma unroll
+        for (int e = 0; e < EARLY; ++e) {
+            const int i = tid + e * SK_THREADS, m = i / cnt;
+            const bool ok = i < MT * 8 * cnt && m < g.M && my_n < g.N;
+            early0[e] = (ok && g.add0) ? g.add0[(size_t)m * g.N + my_n] : 0.f;
+            early1[e] = (ok && g.add1) ? g.add1[(size_t)m * g.N + my_n] : 0.f;
+        }
+    }
     for (int it = 0; it < iters; ++it) {
         if (!mbar_wait(bars + 8 * (it % STAGES), (it / STAGES) & 1)) break;
         __syncthreads();                                      // everyone is done with the stage refilled next
@@ -154,23 +176,30 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
     }
     cluster.sync();
     // this block finishes columns [rank*cnt, (rank+1)*cnt) of the tile, summing the blocks in rank order
-    const int cnt = SK_ROWS / S;
     TO* O = (TO*)g.out;
-    for (int i = tid; i < MT * 8 * cnt; i += SK_THREADS) {
-        const int m = i / cnt, nl = rank * cnt + (i - m * cnt);
-        const int n = n0 + nl;
-        if (m >= g.M || n >= g.N) continue;
+    const int nl = my_n - n0;
+#pragma unroll 1
+    for (int e = 0; e * SK_THREADS + tid < MT * 8 * cnt; ++e) {
+        const int m = (tid + e * SK_THREADS) / cnt;
+        if (m >= g.M || my_n >= g.N) continue;
         float v = 0.f;
         for (int s = 0; s < S; ++s) {
             const float* peer = cluster.map_shared_rank(tile, s);
             v += peer[m * LD + nl];
         }
-        if (g.bias) v += g.bias[n];
-        if (g.bias2) v += g.bias2[n];
-        v = gl_activate<false>(v, g.act);
-        const size_t o = (size_t)m * g.N + n;
-        if (g.add0) v += g.add0[o];
-        if (g.add1) v += g.add1[o];
+        v = gl_activate<false>(v + my_bias, g.act);
+        const size_t o = (size_t)m * g.N + my_n;
+        if constexpr (MT <= 2) {
+            // (indexed with a compile-time number below: the array stays in registers)
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < EARLY; ++q)
+                if (q == e) { a0 = early0[q]; a1 = early1[q]; }
+            v = (v + a0) + a1;
+        } else {
+            if (g.add0) v += g.add0[o];
+            if (g.add1) v += g.add1[o];
+        }
         gl_store(O + o, v);
     }
     cluster.sync();       // nobody leaves while a peer may still read its tile

@@ -9,7 +9,7 @@
 
 // cos/sin of angle float(pos) * inv_freq[i]; the product is taken in 32-bit and
 // the functions in 64-bit, as the reference does (model.go:3041-3046).
-__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
+__global__ void rope_table_kernel(const int* pos, const float* __restrict__ inv_freq,
                                   float* __restrict__ cosv, float* __restrict__ sinv, int T, int half) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     gl_grid_launch_dependents();

@@ -7,8 +7,10 @@
 // ---------------------------------------------------------------------------
 // Embedding: out[t, :] = scale * table[tokens[t], :]          (model.go:2642-2651)
 // ---------------------------------------------------------------------------
+// (tokens, index, x below: what an earlier kernel of the step wrote is not declared restrict: loads through a
+// const restrict pointer count as loads of memory nobody writes, which the compiler may move above the wait)
 template <typename TW>
-__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+__global__ void embed_kernel(const TW* __restrict__ table, const int* tokens,
                              float* __restrict__ out, int D, int V, float scale) {
     const int t = blockIdx.x;
     gl_grid_launch_dependents();
@@ -39,7 +41,7 @@ GL_API int gl_embed(const void* table, int table_dtype, const int* tokens, float
 // absolute positions are added once, before the first layer (model.go:2648-2651).
 // ---------------------------------------------------------------------------
 template <typename TW>
-__global__ void add_rows_kernel(const TW* __restrict__ table, const int* __restrict__ index,
+__global__ void add_rows_kernel(const TW* __restrict__ table, const int* index,
                                 float* __restrict__ out, int D, int N) {
     const int t = blockIdx.x;
     gl_grid_launch_dependents();
@@ -106,14 +108,29 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 // NV: values of the row each thread keeps in registers (the row is read once when it fits)
 template <typename TO, int NV>
-__global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+__global__ void norm_kernel(const float* x, const int* __restrict__ rows,
                             const float* __restrict__ gamma, const float* __restrict__ beta,
                             TO* __restrict__ out, int D, float eps, int rms) {
     __shared__ float red[32];
     __shared__ float s_inv;
     const int r = blockIdx.x;
     gl_grid_launch_dependents();
+    // The norm's own vectors do not depend on the kernel before this one: they are asked for before this
+    // kernel waits for it.  In a decode step they are cold (a layer's vectors are read once a step, with
+    // gigabytes in between), and fetched at the end their trip to memory would stand between two products.
+    float gv[NV > 0 ? NV : 1], bv[NV > 0 ? NV : 1];
+    if (NV > 0) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            gv[i] = d < D ? gamma[d] : 0.f;
+            bv[i] = (d < D && beta) ? beta[d] : 0.f;
+        }
+    }
     gl_grid_wait();
+    // (x is what the kernel before this one wrote: it is read with loads that the compiler may not move
+    // above the wait.  Declared const and restrict, a pointer's loads count as loads of memory that nobody
+    // writes, and those may be issued together with the loads above.)
     const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
     TO* o = out + (size_t)r * D;
     float v[NV > 0 ? NV : 1];
@@ -121,7 +138,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int d = threadIdx.x + i * blockDim.x;
-            v[i] = d < D ? xr[d] : 0.f;
+            v[i] = d < D ? __ldcg(xr + d) : 0.f;
         }
     }
     float mean = 0.f;
@@ -131,7 +148,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__
 #pragma unroll
             for (int i = 0; i < NV; ++i) s += v[i];
         } else {
-            for (int d = threadIdx.x; d < D; d += blockDim.x) s += xr[d];
+            for (int d = threadIdx.x; d < D; d += blockDim.x) s += __ldcg(xr + d);
         }
         mean = block_sum(s, red) / (float)D;
     }
@@ -143,7 +160,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__
             q += c * c;
         }
     } else {
-        for (int d = threadIdx.x; d < D; d += blockDim.x) { const float c = xr[d] - mean; q += c * c; }
+        for (int d = threadIdx.x; d < D; d += blockDim.x) { const float c = __ldcg(xr + d) - mean; q += c * c; }
     }
     const float var = block_sum(q, red) / (float)D;
     // one thread takes the reciprocal square root in 64-bit, as the reference does (bert.go:764)
@@ -154,15 +171,11 @@ __global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int d = threadIdx.x + i * blockDim.x;
-            if (d < D) {
-                float y = (v[i] - mean) * inv * gamma[d];
-                if (beta) y += beta[d];
-                gl_store(o + d, y);
-            }
+            if (d < D) gl_store(o + d, (v[i] - mean) * inv * gv[i] + bv[i]);
         }
     } else {
         for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            float y = (xr[d] - mean) * inv * gamma[d];
+            float y = (__ldcg(xr + d) - mean) * inv * gamma[d];
             if (beta) y += beta[d];
             gl_store(o + d, y);
         }
@@ -173,7 +186,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__
 // statistics need warp shuffles only, loads and stores are 16 bytes (D a multiple of 4).
 template <typename TO, int NV4>
 __global__ void __launch_bounds__(256)
-norm_warp_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gamma,
+norm_warp_kernel(const float* x, const int* __restrict__ rows, const float* __restrict__ gamma,
                  const float* __restrict__ beta, TO* __restrict__ out, int R, int D, float eps, int rms) {
     gl_grid_launch_dependents();
     gl_grid_wait();
