@@ -39,6 +39,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # decode steps (90 ms; 3.05, 2.89, 2.68, 2.52, then 2.45 ms a step were measured): without them a figure
 # would depend on how long ago the prompts ran, which is to say on the caller's --warmup.
 SETTLE_STEPS = 40
+SETTLE_POINT_MS = 150.0      # the least time the extra points (batch 1, batch 64) settle for before they are timed
 
 
 def peaks():
@@ -203,13 +204,19 @@ def main():
         """One more decode measurement as a record: rate, time, bytes and the fraction of the HBM peak.
         ``settle_elsewhere``: the settling steps run on sequences of their own first, for a context too
         short to hold them."""
+        # A point is taken right after other work (the prompts of 64 sequences, the prefill measurement) whose
+        # power-capped clocks take a while to come back: it settles for SETTLE_POINT_MS at least, in steps
+        # counted from the bytes a step reads, and says how many.
+        est_ms = (weight_bytes + batch * context * kv_per_pos) / (0.6 * pk["hbm_gbs"] * 1e9) * 1e3
+        settle = max(S, min(int(SETTLE_POINT_MS / est_ms), context // 4))
         if settle_elsewhere:
-            decode_rate(batch, 1, 1, 8 + S + 3, S=S)
+            decode_rate(batch, 1, 1, 8 + settle + 3, S=settle)
             rate, ms, mid, _ = decode_rate(batch, steps, 3, context, S=0)
         else:
-            rate, ms, mid, _ = decode_rate(batch, steps, W, context)
+            rate, ms, mid, _ = decode_rate(batch, steps, W, context, S=settle)
         nbytes = weight_bytes + batch * mid * kv_per_pos
         return {"value": round(rate, 1), "ms_per_step": round(ms, 4), "batch": batch, "context": context,
+                "settle_steps": settle,
                 "bytes": int(nbytes), "frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
                 "weights_only_frac": round(weight_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
 
@@ -267,6 +274,13 @@ def main():
                      "weights_only_frac": round(weight_bytes / (ms_step / 1e3) / 1e9 / pk["hbm_gbs"], 4)
                      if "decode" in sections else None},
     }
+    # (the points before the prefill: its products run at the power limit, and a small decode step timed
+    # right behind them is timed at clocks that are still coming back)
+    if "points" in sections:
+        detail = {"decode_b1": point(1, min(K, 64), C), "decode_b64": point(64, min(K, 32), C),
+                  "decode_b64_ctx128": point(64, 16, 128, settle_elsewhere=True)}
+        out["points"] = {"decode_b1": detail["decode_b1"]["value"], "decode_b64": detail["decode_b64"]["value"]}
+        out["points_detail"] = detail
     if "prefill" in sections:
         T = 2048
         toks = [int(t) for t in rng.integers(0, V, size=T)]
@@ -293,11 +307,6 @@ def main():
                           "peak": "bf16_tflops (a burst of one product)", "flops": flops,
                           "frac_sustained": round(flops / (ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
                           if pk.get("bf16_tflops_sustained") else None}
-    if "points" in sections:
-        detail = {"decode_b1": point(1, min(K, 64), C), "decode_b64": point(64, min(K, 32), C),
-                  "decode_b64_ctx128": point(64, 16, 128, settle_elsewhere=True)}
-        out["points"] = {"decode_b1": detail["decode_b1"]["value"], "decode_b64": detail["decode_b64"]["value"]}
-        out["points_detail"] = detail
     print(json.dumps(out))
     return 0
 
