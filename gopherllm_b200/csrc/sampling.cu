@@ -360,10 +360,9 @@ sample_kernel(SampleArgs a) {
             }
         }
         __syncthreads();
-        for (int i = tid; i < V; i += SM_THREADS) {
-            const float v = w[i];
+        for_row(w, V, [&](int i, float v) {
             if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-        }
+        });
     }
     block_argmax(bv, bi, s_f, s_i, &s_best, &s_besti);
     const float vmax = s_best;
@@ -386,10 +385,12 @@ sample_kernel(SampleArgs a) {
             __syncthreads();
             const unsigned prefix = s_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = tid; i < V; i += SM_THREADS) {
-                const unsigned key = ordered_key(w[i]);
+            // (eight loads under way per thread: a loop that loads, counts and loads again waits out a trip
+            // to L2 per element, 50 of them a pass)
+            for_row(w, V, [&](int, float pv) {
+                const unsigned key = ordered_key(pv);
                 if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
-            }
+            });
             __syncthreads();
             if (tid == 0) {
                 unsigned need = s_need;
@@ -408,36 +409,59 @@ sample_kernel(SampleArgs a) {
         if (tid == 0) { s_ngt = 0; s_eq = 0; }
         for (int i = tid; i < SM_KMAX; i += SM_THREADS) { c_val[i] = -INFINITY; c_idx[i] = 0x7fffffff; }
         __syncthreads();
-        for (int base = 0; base < V; base += SM_THREADS) {
-            const int i = base + tid;
-            float v = 0.f; unsigned key = 0; bool eq = false;
-            if (i < V) {
-                v = w[i];
-                key = ordered_key(v);
-                if (key > kth) {
-                    const unsigned slot = atomicAdd(&s_ngt, 1u);
-                    c_val[k - 1 - slot] = v;          // filled from the back; sorted below
-                    c_idx[k - 1 - slot] = i;
+        // what lies above the k-th key goes in as it comes (filled from the back; sorted below), and the
+        // elements equal to it are counted: eight loads under way per thread, no barrier inside
+        for_row(w, V, [&](int i, float v) {
+            const unsigned key = ordered_key(v);
+            if (key > kth) {
+                const unsigned slot = atomicAdd(&s_ngt, 1u);
+                c_val[k - 1 - slot] = v;
+                c_idx[k - 1 - slot] = i;
+            } else if (key == kth) {
+                atomicAdd(&s_eq, 1u);
+            }
+        });
+        __syncthreads();
+        const unsigned n_eq = s_eq;
+        __syncthreads();
+        if (tid == 0) s_eq = 0;
+        __syncthreads();
+        if (n_eq <= need_eq) {
+            // every element equal to the k-th key belongs to the set: their order is the sort's business
+            for_row(w, V, [&](int i, float v) {
+                if (ordered_key(v) == kth) {
+                    const unsigned slot = atomicAdd(&s_eq, 1u);
+                    c_val[slot] = v;
+                    c_idx[slot] = i;
                 }
-                eq = key == kth;
+            });
+        } else {
+            // more equals than places (ties at the set's edge): they enter in index order until the set is full
+            for (int base = 0; base < V; base += SM_THREADS) {
+                const int i = base + tid;
+                float v = 0.f; bool eq = false;
+                if (i < V) {
+                    v = w[i];
+                    eq = ordered_key(v) == kth;
+                }
+                const unsigned bal = __ballot_sync(0xffffffffu, eq);
+                const int lane = tid & 31, wp = tid >> 5;
+                __syncthreads();
+                if (lane == 0) s_i[wp] = __popc(bal);
+                __syncthreads();
+                unsigned before = s_eq;
+                for (int q = 0; q < wp; ++q) before += (unsigned)s_i[q];
+                const unsigned mine = before + __popc(bal & ((1u << lane) - 1u));
+                if (eq && mine < need_eq) { c_val[mine] = v; c_idx[mine] = i; }
+                __syncthreads();
+                if (tid == 0) {
+                    unsigned tot = 0;
+                    for (int q = 0; q < SM_THREADS / 32; ++q) tot += (unsigned)s_i[q];
+                    s_eq += tot;
+                }
+                __syncthreads();
+                if (s_eq >= need_eq) break;                // (the same for every thread: read behind the barrier)
             }
-            // elements equal to the k-th key enter in index order until the set is full
-            const unsigned bal = __ballot_sync(0xffffffffu, eq);
-            const int lane = tid & 31, wp = tid >> 5;
-            __syncthreads();
-            if (lane == 0) s_i[wp] = __popc(bal);
-            __syncthreads();
-            unsigned before = s_eq;
-            for (int q = 0; q < wp; ++q) before += (unsigned)s_i[q];
-            const unsigned mine = before + __popc(bal & ((1u << lane) - 1u));
-            if (eq && mine < need_eq) { c_val[mine] = v; c_idx[mine] = i; }
-            __syncthreads();
-            if (tid == 0) {
-                unsigned tot = 0;
-                for (int q = 0; q < SM_THREADS / 32; ++q) tot += (unsigned)s_i[q];
-                s_eq += tot;
-            }
-            __syncthreads();
         }
         // bitonic sort of the candidates, value descending then index ascending
         int kp = 1;
