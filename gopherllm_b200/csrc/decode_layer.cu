@@ -185,9 +185,11 @@ __device__ __forceinline__ float dl_row_bias(const LayerArgs& a, int phase, int 
     return (p.b_out ? p.b_out[n] : 0.f) + (p.b_down ? p.b_down[n] : 0.f);
 }
 
+// `xs_pre`: the residual values of phase 3 where the caller asked for them ahead of the sums (else they are
+// read here).
 template <int NE>
 __device__ __forceinline__ void dl_finish_rows(const LayerArgs& a, int phase, int tile, int nl, int m0, int mend,
-                                               const float (&v)[NE], float b) {
+                                               const float (&v)[NE], float b, const float* xs_pre = nullptr) {
     const DecodeLayerArgs& p = a.p;
     if (phase == 1) {
         const bool up = tile >= a.tiles_q;
@@ -213,7 +215,8 @@ __device__ __forceinline__ void dl_finish_rows(const LayerArgs& a, int phase, in
         if (n >= p.D) return;
         float xs[NE];
 #pragma unroll
-        for (int e = 0; e < NE; ++e) xs[e] = m0 + e < mend ? __ldcg(p.x + (size_t)(m0 + e) * p.D + n) : 0.f;
+        for (int e = 0; e < NE; ++e)
+            xs[e] = xs_pre ? xs_pre[e] : (m0 + e < mend ? __ldcg(p.x + (size_t)(m0 + e) * p.D + n) : 0.f);
 #pragma unroll
         for (int e = 0; e < NE; ++e)
             if (m0 + e < mend) p.x[(size_t)(m0 + e) * p.D + n] = xs[e] + (v[e] + b);
@@ -609,7 +612,13 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
             const int smid = s0 + (s1 - s0 + 1) / 2;
             const int r0 = half ? smid : s0, r1 = half ? s1 : smid;
             for (int m0 = r0; m0 < r1; m0 += 8) {
-                float v[8];
+                float v[8], xs[8];
+                {                                         // the residual values, asked for ahead of the blocks' parts
+                    const int n = tile * DL_ROWS + nl;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                        xs[e] = (phase == 3 && n < p.D && m0 + e < r1) ? __ldcg(p.x + (size_t)(m0 + e) * p.D + n) : 0.f;
+                }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) v[e] = 0.f;
                 for (int sg0 = 0; sg0 < nseg; sg0 += 4) {            // four blocks' parts asked for before the first is added
@@ -624,7 +633,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
 #pragma unroll
                         for (int e = 0; e < 8; ++e) v[e] += t4[u][e];
                 }
-                dl_finish_rows<8>(a, phase, tile, nl, m0, r1, v, row_bias);
+                dl_finish_rows<8>(a, phase, tile, nl, m0, r1, v, row_bias, xs);
             }
             both_sync();
             if (threadIdx.x == 0 && atomicAdd(done + tile, 1) == nseg - 1) {     // the last to finish leaves both as the next call expects them
