@@ -65,6 +65,11 @@ static_assert(GL_HEAD_DIM % 16 == 0 && GL_HEAD_DIM >= 16 && GL_HEAD_DIM <= 128, 
 #define DL_BK 64
 #define DL_ROWS 128
 #define DL_PAGE_BYTES (GL_PAGE * DL_ROWB)   // the keys or the values of one page of one head
+// Rows of a whole number of 128 bytes (head sizes 64 and 128) would put the eight rows of an ldmatrix on
+// the same banks: such pages are brought in as tiles of 64 dims with the 128-byte swizzle (one copy per
+// tile), and every access goes through dl_page_off.  Other row lengths spread over the banks by themselves.
+#define DL_PAGE_SWIZZLED ((DL_ROWB % 128) == 0)
+#define DL_PAGE_TILES (DL_PAGE_SWIZZLED ? DL_HD / 64 : 1)
 #define DL_MAXG 8                     // query heads per key/value head
 #define DL_MAXB 64                    // sequences (= tokens) per step
 #define DL_GEN 32                     // the barrier's generation word, a cache line away from its arrival count
@@ -157,6 +162,12 @@ __device__ __forceinline__ bool dl_grid_wait(const unsigned* bar, unsigned targe
 __device__ __forceinline__ void dl_publish() {
     dl_fence_async_all();
     __threadfence();
+}
+
+// byte offset of 16-byte chunk cc of row r of a page of keys or values in shared memory
+__device__ __forceinline__ int dl_page_off(int r, int cc) {
+    if (DL_PAGE_SWIZZLED) return (cc >> 3) * (GL_PAGE * 128) + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+    return r * DL_ROWB + cc * 16;
 }
 
 __device__ __forceinline__ float dl_cons_sum(float v, float* red, int tid, int bar_id) {   // sum over the 128 consuming threads
@@ -426,7 +437,10 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
                         if (lane == 0) {
                             acquire();
                             if (!second) mbar_expect_tx(full0 + 8 * slot, PAGE_TX);
-                            tma_load_2d(base + slot * DL_STAGE + (second ? DL_PAGE_BYTES : 0), pmap, 0, row, full0 + 8 * slot);
+#pragma unroll
+                            for (int pt = 0; pt < DL_PAGE_TILES; ++pt)
+                                tma_load_2d(base + slot * DL_STAGE + (second ? DL_PAGE_BYTES : 0) + pt * (GL_PAGE * 128), pmap,
+                                            pt * 64, row, full0 + 8 * slot);
                         }
                         advance();
                     }
@@ -716,13 +730,13 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
                         const __nv_bfloat16* head = qkv_b + ((size_t)p.nH + (size_t)is_v * p.nKV + g) * DL_HD;
                         const uint4 val = ad_rotated_chunk(head, cc, is_v ? 0 : p.half, is_v ? nullptr : cs,
                                                            is_v ? nullptr : sn, 1.0f);
-                        *(uint4*)((is_v ? sV : sK) + r * DL_ROWB + cc * 16) = val;
+                        *(uint4*)((is_v ? sV : sK) + dl_page_off(r, cc)) = val;
                         const int id = gl_checked(p.pages[(size_t)b * p.max_pages + gl_checked(pabs, p.max_pages, GL_BAD_POSITION)], p.n_pages, GL_BAD_PAGE);
                         __nv_bfloat16* cache = (__nv_bfloat16*)(is_v ? p.v_cache : p.k_cache);
                         *(uint4*)(cache + (size_t)id * page_stride + head_off + (size_t)r * DL_HD + cc * 8) = val;
                     }
                     for (int i = tid; i < (GL_PAGE - 1 - r) * DL_CHUNKS; i += DL_CONS)
-                        *(uint4*)(sV + (r + 1) * DL_ROWB + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        *(uint4*)(sV + dl_page_off(r + 1 + i / DL_CHUNKS, i % DL_CHUNKS)) = make_uint4(0u, 0u, 0u, 0u);
                     fence_proxy_async();                  // these writes before the stage's next load
                     cons_sync();
                 }
@@ -734,7 +748,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
                         unsigned af[4];
                         const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
                         const int cc = kk * 2 + (lane >> 4);
-                        ad_ldm4(Ks + r * DL_ROWB + cc * 16, af);
+                        ad_ldm4(Ks + dl_page_off(r, cc), af);
                         ad_mma(s4, af, qb[kk][0], qb[kk][1]);
                     }
                     {
@@ -776,7 +790,7 @@ decode_layer_kernel(const __grid_constant__ LayerArgs a) {
                         unsigned vf[4];
                         const int r = warp * 16 + (lane >> 4) * 8 + (lane & 7);
                         const int cc = dt * 2 + ((lane >> 3) & 1);
-                        ad_ldm4t(Vs + r * DL_ROWB + cc * 16, vf);
+                        ad_ldm4t(Vs + dl_page_off(r, cc), vf);
                         ad_mma(o[dt], vf, pb0, pb1);
                     }
                 }
@@ -881,11 +895,11 @@ static int dl_plain_map(CUtensorMap* map, const void* base, uint64_t rows, uint3
     if (((uintptr_t)base & 15) || (cols * 2) % 16) return GL_ERR_ALIGN;
     cuuint64_t dims[2] = {cols, rows};
     cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {cols, GL_PAGE};
+    cuuint32_t box[2] = {DL_PAGE_SWIZZLED ? 64u : cols, GL_PAGE};       // (swizzled pages: a tile of 64 dims a copy)
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, DL_PAGE_SWIZZLED ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? GL_OK : GL_ERR_DRIVER;
 }
 

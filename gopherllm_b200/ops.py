@@ -630,6 +630,11 @@ DECODE_LAYER_MAX_ROWS = 64
 # 1.92 / 2.21, 16 tokens 2.46 / 2.72, 17 tokens 2.83 / 2.79, 32 tokens 3.81 / 3.61 (1,024 positions each);
 # 64 tokens of 128 positions 3.54 / 2.69, of 300 4.48 / 3.50, of 2,048 9.60 / 8.46.
 DECODE_LAYER_MIN_ROWS = 17
+# ... where the first products' 128-row tiles fill the SMs one to a block (Phi-2: 140 tiles on 148 SMs).
+# Where they do not (Phi-1.5: 112 tiles), the tiles are cut between blocks and finished through scratch, and
+# the separate kernels stay ahead up to 32 tokens (Phi-1.5's sizes, 1,024 positions: 17 tokens 1.68 / 1.95,
+# 32 tokens 2.27 / 2.43, 33 tokens 2.67 / 2.58, 56 tokens 3.44 / 3.28, 64 tokens of 2,048 5.55 / 5.36).
+DECODE_LAYER_MIN_ROWS_CUT_TILES = 33
 # ... and steps whose longest sequence is shorter than this (none: the fused layer is ahead at every
 # context length from 17 tokens on).
 DECODE_LAYER_MIN_CONTEXT = 0
@@ -642,11 +647,16 @@ _DECODE_LAYER_SYNC: dict = {}      # device index -> the int32 words the fused l
 def decode_layer_takes(x, w_qkv, w_up, w_out, w_down, cache_dtype, head_dim: int, group: int, rotary_half: int,
                        interleaved: bool, head_norm: bool, longest: int = 1 << 30) -> bool:
     """Whether the fused decode layer takes these types and sizes (the caller falls back to the separate
-    kernels otherwise): bfloat16 weights and cache, DECODE_LAYER_MIN_ROWS to 64 tokens, a longest sequence
+    kernels otherwise): bfloat16 weights and cache, DECODE_LAYER_MIN_ROWS (or, where the first products' tiles do
+    not fill the SMs one to a block, DECODE_LAYER_MIN_ROWS_CUT_TILES) to 64 tokens, a longest sequence
     (``longest``, positions after the step) of at least DECODE_LAYER_MIN_CONTEXT, head sizes up to 128 in steps of 16,
     up to 8 query heads per key/value head, split-half rotation over a multiple of 16 dims, no per-head
     norm, widths that are multiples of 8."""
-    return (USE_DECODE_LAYER and DECODE_LAYER_MIN_ROWS <= x.shape[0] <= DECODE_LAYER_MAX_ROWS
+    tiles = -(-w_qkv.shape[0] // 128) + -(-w_up.shape[0] // 128)
+    blocks = sm_count(x.device)
+    whole_tiles = tiles * 10 >= blocks * -(-tiles // blocks) * 9
+    fewest = DECODE_LAYER_MIN_ROWS if whole_tiles else max(DECODE_LAYER_MIN_ROWS, DECODE_LAYER_MIN_ROWS_CUT_TILES)
+    return (USE_DECODE_LAYER and fewest <= x.shape[0] <= DECODE_LAYER_MAX_ROWS
             and longest >= DECODE_LAYER_MIN_CONTEXT and cache_dtype == torch.bfloat16
             and all(w.dtype == torch.bfloat16 for w in (w_qkv, w_up, w_out, w_down))
             and head_dim % 16 == 0 and head_dim <= DECODE_LAYER_MAX_HEAD_DIM and group <= DECODE_MAX_GROUP

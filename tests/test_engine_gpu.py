@@ -242,12 +242,12 @@ def test_captured_steps_are_kept_up_to_a_limit():
 
 @pytest.fixture
 def fused_layer_for_any_batch():
-    """The fused decode layer is taken for more than 32 tokens by default; these tests want it from one."""
+    """The fused decode layer is taken from 17 or 33 tokens on by default; these tests want it from one."""
     from gopherllm_b200 import ops
-    old = ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT
-    ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT = 1, 1
+    old = ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT, ops.DECODE_LAYER_MIN_ROWS_CUT_TILES
+    ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT, ops.DECODE_LAYER_MIN_ROWS_CUT_TILES = 1, 1, 1
     yield ops
-    ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT = old
+    ops.DECODE_LAYER_MIN_ROWS, ops.DECODE_LAYER_MIN_CONTEXT, ops.DECODE_LAYER_MIN_ROWS_CUT_TILES = old
 
 
 def test_fused_decode_layer_whole_then_one_by_one(fused_layer_for_any_batch):
