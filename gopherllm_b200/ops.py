@@ -660,6 +660,9 @@ def decode_layer_takes(x, w_qkv, w_up, w_out, w_down, cache_dtype, head_dim: int
             and longest >= DECODE_LAYER_MIN_CONTEXT and cache_dtype == torch.bfloat16
             and all(w.dtype == torch.bfloat16 for w in (w_qkv, w_up, w_out, w_down))
             and head_dim % 16 == 0 and head_dim <= DECODE_LAYER_MAX_HEAD_DIM and group <= DECODE_MAX_GROUP
+            # (head sizes 32 and 96: rows of 64 and 192 bytes put four rows of an ldmatrix on the same banks and
+            # are not swizzled by the kernel; the separate kernels take those)
+            and (head_dim % 32 != 0 or head_dim % 64 == 0)
             and rotary_half % 8 == 0 and not interleaved and not head_norm
             and x.shape[1] % 8 == 0 and w_up.shape[0] % 8 == 0 and w_out.shape[1] % 8 == 0)
 

@@ -115,7 +115,7 @@ def far_key_prompt(rng, n, at=3):
 # A configuration the fused decode layer takes: no per-head norm, a rotary part that is a multiple of
 # 16 dims, grouped key/value heads, sizes that are no powers of two.
 TINY_D = dict(architectures=["PhiForCausalLM"], model_type="phi", num_hidden_layers=3, hidden_size=168,
-              num_attention_heads=6, num_key_value_heads=2, head_dim=32, intermediate_size=200,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=200,
               vocab_size=333, partial_rotary_factor=0.5, rope_theta=10000.0, layer_norm_eps=1e-5,
               hidden_act="gelu_new", qk_layernorm=False, tie_word_embeddings=False,
               max_position_embeddings=320, initializer_range=0.05, torch_dtype="bfloat16", eos_token_id=3)
