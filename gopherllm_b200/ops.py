@@ -630,10 +630,11 @@ DECODE_LAYER_MAX_ROWS = 64
 # 1.92 / 2.21, 16 tokens 2.46 / 2.72, 17 tokens 2.83 / 2.79, 32 tokens 3.81 / 3.61 (1,024 positions each);
 # 64 tokens of 128 positions 3.54 / 2.69, of 300 4.48 / 3.50, of 2,048 9.60 / 8.46.
 DECODE_LAYER_MIN_ROWS = 17
-# ... where the first products' 128-row tiles fill the SMs one to a block (Phi-2: 140 tiles on 148 SMs).
-# Where they do not (Phi-1.5: 112 tiles), the tiles are cut between blocks and finished through scratch, and
-# the separate kernels stay ahead up to 32 tokens (Phi-1.5's sizes, 1,024 positions: 17 tokens 1.68 / 1.95,
-# 32 tokens 2.27 / 2.43, 33 tokens 2.67 / 2.58, 56 tokens 3.44 / 3.28, 64 tokens of 2,048 5.55 / 5.36).
+# ... where the first products' 128-row tiles nearly fill the SMs one to a block (Phi-2: 140 tiles on 148
+# SMs).  Where they do not (Phi-1.5: 112 tiles), part of the machine idles through that phase and the separate
+# kernels stay ahead up to 32 tokens (Phi-1.5's sizes, 1,024 positions, separate / fused: 17 tokens 1.68 / 1.80,
+# 24 tokens 1.94 / 2.08, 32 tokens 2.27 / 2.28, 33 tokens 2.68 / 2.39, 48 tokens 3.07 / 2.87, 64 tokens of
+# 2,048 positions 5.57 / 5.15).
 DECODE_LAYER_MIN_ROWS_CUT_TILES = 33
 # ... and steps whose longest sequence is shorter than this (none: the fused layer is ahead at every
 # context length from 17 tokens on).
